@@ -1,0 +1,415 @@
+// extern "C" boundary of the library: validation, layout normalisation, kernel choice and launch.
+//
+// Host-side counterpart of the reference's device::Srgemm (include/cuasr/gemm/device/srgemm.h:85-357 and
+// its column-major specialisation :398-567) and device::SrgemmSplitKParallel
+// (include/cuasr/gemm/device/srgemm_splitk_parallel.h:101-378, :424-607).
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/cuasr_b200.h"
+#include "srgemm_launch.h"
+
+namespace cuasr_b200 {
+namespace {
+
+std::atomic<uint64_t> g_launches{0};
+thread_local const char* t_last_kernel = "none";
+
+// ---- per-device state: SM count and the device status word --------------------------------------
+__device__ unsigned int g_status_word;  // zero-initialised when the module loads
+
+struct DeviceState {
+  bool ready = false;
+  int sms = 0;
+  unsigned int* status = nullptr;
+};
+constexpr int kMaxDevices = 64;
+DeviceState g_devices[kMaxDevices];
+std::mutex g_device_mutex;
+
+// First call on a device looks up the SM count and the address of the status word; no allocation.
+bool device_state(DeviceState** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  DeviceState& st = g_devices[dev];
+  if (!st.ready) {
+    if (cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return false;
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_status_word) != cudaSuccess) return false;
+    st.status = static_cast<unsigned int*>(addr);
+    st.ready = true;
+  }
+  *out = &st;
+  return true;
+}
+
+// ---- cuTensorMapEncodeTiled through the runtime, so that the library does not link libcuda --------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+template <typename T> struct TmaType;
+template <> struct TmaType<float>    { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; };
+template <> struct TmaType<double>   { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_FLOAT64; };
+template <> struct TmaType<int32_t>  { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_INT32; };
+template <> struct TmaType<uint32_t> { static constexpr CUtensorMapDataType v = CU_TENSOR_MAP_DATA_TYPE_UINT32; };
+
+// Describes one operand of `rows` x K elements to TMA.
+//   K-contiguous:  tensor {K, rows}, box {128 bytes of k, 128 rows}, 128-byte swizzle
+//   MN-contiguous: tensor {rows, K}, box {128 rows, 128 bytes worth of k}, no swizzle
+template <typename T>
+bool make_operand_map(CUtensorMap* map, const T* ptr, long long ld, int rows, int K, bool kcontig, bool nan_fill) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint32_t tk = kTileKBytes / sizeof(T);
+  cuuint64_t dims[2];
+  cuuint32_t box[2];
+  if (kcontig) { dims[0] = K; dims[1] = rows; box[0] = tk; box[1] = kTileM; }
+  else         { dims[0] = rows; dims[1] = K; box[0] = kTileM; box[1] = tk; }
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(T)};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = encode(map, TmaType<T>::v, 2, const_cast<T*>(ptr), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            kcontig ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            nan_fill ? CU_TENSOR_MAP_FLOAT_OOB_FILL_NAN_REQUEST_ZERO_FMA
+                                     : CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// ---- host evaluation of ring operators (only for the "is C needed" decision) ----------------------
+template <typename T>
+T host_op(int op, T l, T r) {
+  switch (op) {
+    case CUASR_OP_PLUS: return l + r;
+    case CUASR_OP_MULTIPLIES: return l * r;
+    case CUASR_OP_MINIMUM: return r < l ? r : l;
+    case CUASR_OP_MAXIMUM: return l < r ? r : l;
+    case CUASR_OP_BINARY_AND: return static_cast<T>(l && r);
+    case CUASR_OP_BINARY_OR: return static_cast<T>(l || r);
+    default: break;
+  }
+  if constexpr (std::is_integral<T>::value) {
+    switch (op) {
+      case CUASR_OP_BIT_AND: return l & r;
+      case CUASR_OP_BIT_OR: return l | r;
+      case CUASR_OP_BIT_XOR: return l ^ r;
+      default: break;
+    }
+  }
+  return l;
+}
+
+template <typename T>
+T load_scalar(const cuasr_b200_scalar_t& s) {
+  T v;
+  std::memcpy(&v, s.bytes, sizeof(T));
+  return v;
+}
+
+bool ring_supported(int add, int mul, int dtype) {
+  const bool is_int = (dtype == CUASR_S32 || dtype == CUASR_U32);
+  auto is = [&](int a, int m) { return add == a && mul == m; };
+  if (is(CUASR_OP_PLUS, CUASR_OP_MULTIPLIES) || is(CUASR_OP_MINIMUM, CUASR_OP_PLUS) ||
+      is(CUASR_OP_MAXIMUM, CUASR_OP_PLUS) || is(CUASR_OP_MINIMUM, CUASR_OP_MAXIMUM) ||
+      is(CUASR_OP_MAXIMUM, CUASR_OP_MINIMUM) || is(CUASR_OP_MINIMUM, CUASR_OP_MULTIPLIES) ||
+      is(CUASR_OP_MAXIMUM, CUASR_OP_MULTIPLIES) || is(CUASR_OP_BINARY_OR, CUASR_OP_BINARY_AND))
+    return true;
+  if (is_int && (is(CUASR_OP_BIT_XOR, CUASR_OP_BIT_AND) || is(CUASR_OP_BIT_OR, CUASR_OP_BIT_AND) ||
+                 is(CUASR_OP_BIT_XOR, CUASR_OP_BINARY_AND)))
+    return true;
+  return false;
+}
+
+// The problem after the column-major-C transposition of device/srgemm.h:432-453, :513-523: always a
+// row-major D (m x n), A' (m x k) and B' (k x n), each operand either K-contiguous or MN-contiguous.
+struct Normalised {
+  int m, n, k;
+  const void* a; long long lda; bool a_kcontig;
+  const void* b; long long ldb; bool b_kcontig;
+  const void* c; long long ldc;
+  void* d;       long long ldd;
+};
+
+Normalised normalise(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args) {
+  Normalised p;
+  p.k = args.k;
+  p.c = args.C; p.ldc = args.ldc; p.d = args.D; p.ldd = args.ldd;
+  if (desc.layout_c == CUASR_ROW_MAJOR) {
+    p.m = args.m; p.n = args.n;
+    p.a = args.A; p.lda = args.lda; p.a_kcontig = (desc.layout_a == CUASR_ROW_MAJOR);
+    p.b = args.B; p.ldb = args.ldb; p.b_kcontig = (desc.layout_b == CUASR_COLUMN_MAJOR);
+  } else {
+    // D^T = B^T (x)(+) A^T; a column-major matrix is the row-major storage of its transpose
+    p.m = args.n; p.n = args.m;
+    p.a = args.B; p.lda = args.ldb; p.a_kcontig = (desc.layout_b == CUASR_COLUMN_MAJOR);
+    p.b = args.A; p.ldb = args.lda; p.b_kcontig = (desc.layout_a == CUASR_ROW_MAJOR);
+  }
+  return p;
+}
+
+int validate(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  if (desc == nullptr || args == nullptr) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (desc->dtype < CUASR_F32 || desc->dtype > CUASR_U32) return CUASR_STATUS_ERROR_INVALID_DATA_TYPE;
+  for (int l : {desc->layout_a, desc->layout_b, desc->layout_c})
+    if (l != CUASR_ROW_MAJOR && l != CUASR_COLUMN_MAJOR) return CUASR_STATUS_ERROR_INVALID_LAYOUT;
+  if (!ring_supported(desc->add_op, desc->mul_op, desc->dtype)) return CUASR_STATUS_ERROR_NOT_SUPPORTED;
+  if (args->m <= 0 || args->n <= 0 || args->k <= 0) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (args->split_k_slices < 1) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (args->A == nullptr || args->B == nullptr || args->D == nullptr) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  // a leading dimension shorter than the contiguous extent would make rows overlap
+  const long long a_min = desc->layout_a == CUASR_ROW_MAJOR ? args->k : args->m;
+  const long long b_min = desc->layout_b == CUASR_ROW_MAJOR ? args->n : args->k;
+  const long long c_min = desc->layout_c == CUASR_ROW_MAJOR ? args->n : args->m;
+  if (args->lda < a_min || args->ldb < b_min || args->ldd < c_min) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (args->C != nullptr && args->ldc < c_min) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  const size_t es = desc->dtype == CUASR_F64 ? 8 : 4;
+  for (const void* ptr : {args->A, args->B, args->C, static_cast<const void*>(args->D)})
+    if (reinterpret_cast<uintptr_t>(ptr) % es != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+  return CUASR_STATUS_SUCCESS;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Workspace layout for a split over `slices`: [tickets: one u32 per 128 x 128 tile, padded to 256 B]
+// [partials: slices * m * n elements].
+size_t splitk_workspace_bytes(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args) {
+  if (args.split_k_slices <= 1) return 0;
+  const size_t es = desc.dtype == CUASR_F64 ? 8 : 4;
+  const size_t tiles = static_cast<size_t>((args.m + kTileM - 1) / kTileM + 1) * ((args.n + kTileN - 1) / kTileN + 1);
+  return align_up(tiles * sizeof(unsigned int), 256) + es * static_cast<size_t>(args.m) * args.n * args.split_k_slices;
+}
+
+// Dispatch over rings.  X(ADD, MUL) is expanded for each ring the element type supports.
+#define CUASR_FLOAT_RINGS(X)                   \
+  X(CUASR_OP_PLUS, CUASR_OP_MULTIPLIES)        \
+  X(CUASR_OP_MINIMUM, CUASR_OP_PLUS)           \
+  X(CUASR_OP_MAXIMUM, CUASR_OP_PLUS)           \
+  X(CUASR_OP_MINIMUM, CUASR_OP_MAXIMUM)        \
+  X(CUASR_OP_MAXIMUM, CUASR_OP_MINIMUM)        \
+  X(CUASR_OP_MINIMUM, CUASR_OP_MULTIPLIES)     \
+  X(CUASR_OP_MAXIMUM, CUASR_OP_MULTIPLIES)     \
+  X(CUASR_OP_BINARY_OR, CUASR_OP_BINARY_AND)
+#define CUASR_BIT_RINGS(X)                     \
+  X(CUASR_OP_BIT_XOR, CUASR_OP_BIT_AND)        \
+  X(CUASR_OP_BIT_OR, CUASR_OP_BIT_AND)         \
+  X(CUASR_OP_BIT_XOR, CUASR_OP_BINARY_AND)
+
+template <typename T>
+int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int slices) {
+  DeviceState* dev = nullptr;
+  if (!device_state(&dev)) return CUASR_STATUS_ERROR_INTERNAL;
+  cudaStream_t stream = static_cast<cudaStream_t>(args.stream);
+  const Normalised p = normalise(desc, args);
+
+  const T alpha = load_scalar<T>(args.alpha), beta = load_scalar<T>(args.beta);
+  const T add_id = load_scalar<T>(args.add_identity), mul_id = load_scalar<T>(args.mul_identity);
+  // semiring_linear_combination.h:118-125: C is read unless mult(beta, mult-identity) is the add-identity
+  const bool read_c = !(host_op<T>(desc.mul_op, beta, mul_id) == add_id);
+  if (read_c && p.c == nullptr) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+
+  // split-K scratch
+  unsigned int* tickets = nullptr;
+  T* partial = nullptr;
+  if (slices > 1) {
+    const size_t need = splitk_workspace_bytes(desc, args);
+    if (args.workspace == nullptr) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
+    if (args.workspace_bytes < need) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+    const size_t tiles = static_cast<size_t>((args.m + kTileM - 1) / kTileM + 1) * ((args.n + kTileN - 1) / kTileN + 1);
+    const size_t ticket_bytes = align_up(tiles * sizeof(unsigned int), 256);
+    tickets = static_cast<unsigned int*>(args.workspace);
+    partial = reinterpret_cast<T*>(static_cast<char*>(args.workspace) + ticket_bytes);
+    // same role as the semaphore memset of device/srgemm.h:253-259
+    if (cudaMemsetAsync(tickets, 0, ticket_bytes, stream) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+  }
+
+  constexpr int TK = kTileKBytes / sizeof(T);
+  const bool is_float = std::is_floating_point<T>::value;
+  const bool min_or_max = desc.add_op == CUASR_OP_MINIMUM || desc.add_op == CUASR_OP_MAXIMUM;
+  const bool zero_pad_ok =
+      (desc.add_op == CUASR_OP_PLUS && desc.mul_op == CUASR_OP_MULTIPLIES) ||
+      ((desc.add_op == CUASR_OP_BIT_OR || desc.add_op == CUASR_OP_BIT_XOR) &&
+       (desc.mul_op == CUASR_OP_BINARY_AND || desc.mul_op == CUASR_OP_BIT_AND)) ||
+      (desc.add_op == CUASR_OP_BINARY_OR && desc.mul_op == CUASR_OP_BINARY_AND && (add_id == T(0) || add_id == T(1)));
+  const bool nan_pad = is_float && min_or_max;
+  const bool paddable = nan_pad || zero_pad_ok || (p.k % TK == 0);
+  auto tma_ok = [&](const void* ptr, long long ld) {
+    return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && (ld * (long long)sizeof(T)) % 16 == 0;
+  };
+  const bool small = static_cast<long long>(p.m) * p.n < 64 * 64;
+  bool use_tma = paddable && !small && tma_ok(p.a, p.lda) && tma_ok(p.b, p.ldb) && encode_tiled_fn() != nullptr;
+
+  cudaError_t err = cudaErrorInvalidValue;
+  bool launched = false;
+  if (use_tma) {
+    CUtensorMap map_a, map_b;
+    if (make_operand_map<T>(&map_a, static_cast<const T*>(p.a), p.lda, p.m, p.k, p.a_kcontig, nan_pad) &&
+        make_operand_map<T>(&map_b, static_cast<const T*>(p.b), p.ldb, p.n, p.k, p.b_kcontig, nan_pad)) {
+      TmaParams<T> tp;
+      tp.M = p.m; tp.N = p.n; tp.K = p.k;
+      tp.C = static_cast<const T*>(p.c); tp.ldc = p.ldc;
+      tp.D = static_cast<T*>(p.d); tp.ldd = p.ldd;
+      tp.alpha = alpha; tp.beta = beta; tp.add_identity = add_id; tp.read_c = read_c;
+      tp.tiles_m = (p.m + kTileM - 1) / kTileM; tp.tiles_n = (p.n + kTileN - 1) / kTileN;
+      tp.status = dev->status;
+      tp.slices = slices;
+      const int k_tiles = (p.k + TK - 1) / TK;
+      tp.k_tiles_per_slice = (k_tiles + slices - 1) / slices;
+      tp.partial = partial; tp.tickets = tickets;
+      const long long work = static_cast<long long>(tp.tiles_m) * tp.tiles_n * slices;
+      const int grid = static_cast<int>(work < dev->sms ? work : dev->sms);
+#define X(ADD, MUL)                                                                                       \
+      if (!launched && desc.add_op == ADD && desc.mul_op == MUL) {                                        \
+        if constexpr (tma_instantiated<ADD, MUL, T>()) {                                                  \
+          err = launch_tma<ADD, MUL, T>(p.a_kcontig, p.b_kcontig, map_a, map_b, tp, grid, stream);        \
+          launched = true;                                                                                \
+        }                                                                                                 \
+      }
+      CUASR_FLOAT_RINGS(X)
+      if constexpr (std::is_integral<T>::value) { CUASR_BIT_RINGS(X) }
+#undef X
+      if (launched) t_last_kernel = slices > 1 ? "tma_splitk" : "tma";
+    }
+  }
+  if (!launched) {
+    GenericParams<T> gp;
+    gp.M = p.m; gp.N = p.n; gp.K = p.k;
+    gp.A = static_cast<const T*>(p.a); gp.a_row = p.a_kcontig ? p.lda : 1; gp.a_col = p.a_kcontig ? 1 : p.lda;
+    gp.B = static_cast<const T*>(p.b); gp.b_row = p.b_kcontig ? 1 : p.ldb; gp.b_col = p.b_kcontig ? p.ldb : 1;
+    gp.C = static_cast<const T*>(p.c); gp.ldc = p.ldc;
+    gp.D = static_cast<T*>(p.d); gp.ldd = p.ldd;
+    gp.alpha = alpha; gp.beta = beta; gp.add_identity = add_id; gp.read_c = read_c;
+    gp.k_per_slice = (p.k + slices - 1) / slices;
+    gp.partial = slices > 1 ? partial : nullptr;
+#define X(ADD, MUL)                                                   \
+    if (!launched && desc.add_op == ADD && desc.mul_op == MUL) {      \
+      err = launch_generic<ADD, MUL, T>(gp, slices, stream);          \
+      launched = true;                                                \
+    }
+    CUASR_FLOAT_RINGS(X)
+    if constexpr (std::is_integral<T>::value) { CUASR_BIT_RINGS(X) }
+#undef X
+    if (launched && err == cudaSuccess && slices > 1) {
+      g_launches.fetch_add(1);
+      bool reduced = false;
+#define X(ADD, MUL)                                                   \
+      if (!reduced && desc.add_op == ADD && desc.mul_op == MUL) {     \
+        err = launch_generic_reduce<ADD, MUL, T>(gp, slices, stream); \
+        reduced = true;                                               \
+      }
+      CUASR_FLOAT_RINGS(X)
+      if constexpr (std::is_integral<T>::value) { CUASR_BIT_RINGS(X) }
+#undef X
+    }
+    if (launched) t_last_kernel = slices > 1 ? "generic_splitk" : "generic";
+  }
+  if (!launched) return CUASR_STATUS_ERROR_NOT_SUPPORTED;
+  if (err != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+  g_launches.fetch_add(1);
+  return CUASR_STATUS_SUCCESS;
+}
+
+int run(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args, int slices) {
+  switch (desc->dtype) {
+    case CUASR_F32: return run_typed<float>(*desc, *args, slices);
+    case CUASR_F64: return run_typed<double>(*desc, *args, slices);
+    case CUASR_S32: return run_typed<int32_t>(*desc, *args, slices);
+    case CUASR_U32: return run_typed<uint32_t>(*desc, *args, slices);
+    default: return CUASR_STATUS_ERROR_INVALID_DATA_TYPE;
+  }
+}
+
+}  // namespace
+}  // namespace cuasr_b200
+
+using namespace cuasr_b200;
+
+extern "C" {
+
+int cuasr_b200_srgemm_can_implement(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  const int st = validate(desc, args);
+  if (st != CUASR_STATUS_SUCCESS) return st;
+  // device/srgemm.h:198-200
+  if (!desc->split_k_serial && args->split_k_slices > 1) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  return CUASR_STATUS_SUCCESS;
+}
+
+size_t cuasr_b200_srgemm_workspace_size(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  if (desc == nullptr || args == nullptr) return 0;
+  if (desc->split_k_serial && args->split_k_slices > 1) return splitk_workspace_bytes(*desc, *args);
+  return 0;
+}
+
+int cuasr_b200_srgemm(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  const int st = cuasr_b200_srgemm_can_implement(desc, args);
+  if (st != CUASR_STATUS_SUCCESS) return st;
+  return run(desc, args, args->split_k_slices);
+}
+
+int cuasr_b200_srgemm_splitk_can_implement(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  return validate(desc, args);
+}
+
+size_t cuasr_b200_srgemm_splitk_workspace_size(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  if (desc == nullptr || args == nullptr) return 0;
+  return splitk_workspace_bytes(*desc, *args);
+}
+
+int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  const int st = validate(desc, args);
+  if (st != CUASR_STATUS_SUCCESS) return st;
+  // device/srgemm_splitk_parallel.h:247-249
+  if (args->split_k_slices > 1 && args->workspace == nullptr) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
+  return run(desc, args, args->split_k_slices);
+}
+
+int cuasr_b200_device_status(void* stream) {
+  DeviceState* dev = nullptr;
+  if (!device_state(&dev)) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned int host = 0;
+  if (cudaMemcpyAsync(&host, dev->status, sizeof(host), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+  if (host != 0) cudaMemsetAsync(dev->status, 0, sizeof(unsigned int), s);
+  return static_cast<int>(host);
+}
+
+const char* cuasr_b200_last_kernel(void) { return t_last_kernel; }
+
+uint64_t cuasr_b200_launch_count(void) { return g_launches.load(); }
+
+const char* cuasr_b200_status_string(int status) {
+  switch (status) {
+    case CUASR_STATUS_SUCCESS: return "success";
+    case CUASR_STATUS_ERROR_MISALIGNED_OPERAND: return "misaligned operand";
+    case CUASR_STATUS_ERROR_INVALID_DATA_TYPE: return "invalid data type";
+    case CUASR_STATUS_ERROR_INVALID_LAYOUT: return "invalid layout";
+    case CUASR_STATUS_ERROR_INVALID_PROBLEM: return "invalid problem";
+    case CUASR_STATUS_ERROR_NOT_SUPPORTED: return "not supported";
+    case CUASR_STATUS_ERROR_WORKSPACE_NULL: return "workspace null";
+    case CUASR_STATUS_ERROR_INTERNAL: return "internal error";
+    default: return "unknown status";
+  }
+}
+
+const char* cuasr_b200_version(void) { return "cuasr_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

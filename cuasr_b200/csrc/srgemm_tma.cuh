@@ -1,0 +1,323 @@
+// The B200 SRGEMM kernel: D = (alpha (x) (A (x)(+) B)) (+) (beta (x) C), row-major D.
+//
+// It replaces, as one kernel, the reference's kernel::Srgemm (include/cuasr/gemm/kernel/srgemm.h:156-321),
+// its threadblock mainloop SrmmaPipelined (include/cuasr/gemm/threadblock/srmma_pipelined.h:153-288),
+// the warp/thread level (include/cuasr/gemm/warp/srmma_simt.h:139-199,
+// include/cuasr/gemm/thread/srmma_sm50.h:118-146) and the epilogue functor
+// (include/cuasr/gemm/epilogue/thread/semiring_linear_combination.h:118-183); with `partial` set it is
+// also the first half of kernel::SrgemmSplitKParallel (include/cuasr/gemm/kernel/srgemm_splitk_parallel.h:86-219).
+//
+// Structure (one persistent CTA per SM, 12 warps = 2 consumer warpgroups + 1 producer warpgroup that
+// hands most of its registers to the consumers with setmaxnreg):
+//   warp 8, lane 0      producer: for every K tile of every output tile this CTA owns, waits for a free
+//                       stage and issues two TMA tile loads (A, B) that complete on the stage's mbarrier.
+//   warps 0..7          consumers: 2 x 4 warps over a 128 x 128 output tile, 8 x 4 lanes per warp, an
+//                       8 x 8 register micro-tile per lane.  They wait for a stage, read 16-byte vectors
+//                       from shared memory and run the contraction two k steps at a time:
+//                       acc = add(acc, a0 (x) b0, a1 (x) b1)  — for fp32 min/max rings one add per product
+//                       plus ONE three-input min/max per two products.
+// Shared-memory tile layouts (per stage, 16 KiB per operand):
+//   K-contiguous operand  (row-major A, column-major B): [128 rows][128 bytes of k], TMA 128-byte swizzle;
+//                         a lane owns rows lane_row + 8 i (A) / lane_col + 4 j (B) and loads 16 bytes of k.
+//   MN-contiguous operand (column-major A, row-major B): [k][128 rows], no swizzle; a lane owns groups of
+//                         16/sizeof(T) adjacent rows and loads one k of a group per 16-byte vector.
+// Ragged edges: TMA fills out-of-range elements with NaN (fp min/max rings; min/max never select a NaN
+// product) or zero (rings where 0 (x) 0 is neutral); stores are predicated on m < M, n < N.
+#pragma once
+
+#include "ring.cuh"
+
+namespace cuasr_b200 {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 128;
+constexpr int kTileKBytes = 128;                 // bytes of k per stage and row
+constexpr int kStages = 5;
+constexpr int kConsumerWarps = 8;
+constexpr int kProducerWarps = 4;                 // one warpgroup; only its first lane issues TMA
+constexpr int kTmaThreads = (kConsumerWarps + kProducerWarps) * 32;
+// Register budget per thread after the warpgroups re-balance with setmaxnreg: the two consumer warps and
+// the one producer warp that share an SM sub-partition fit its 16384 registers (2 * 232 + 40 = 504 <= 512).
+constexpr int kConsumerRegs = 232;
+constexpr int kProducerRegs = 40;
+constexpr int kOperandStageBytes = kTileM * kTileKBytes;   // 16 KiB
+constexpr int kStageBytes = 2 * kOperandStageBytes;
+constexpr int kTmaSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+
+template <typename T>
+struct TmaParams {
+  int M, N, K;
+  const T* C;  long long ldc;   // row-major; may alias D; may be null when !read_c
+  T* D;        long long ldd;   // row-major
+  T alpha, beta, add_identity;
+  int read_c;
+  int tiles_m, tiles_n;
+  unsigned int* status;         // device status word (see DeviceStatus)
+  // split-K (slices > 1): slice z handles K tiles [z * k_tiles_per_slice, ...), the last slice takes the
+  // rest; raw accumulators go to partial + z * M * N (row-major, ld = N).  tickets[tile] counts the
+  // slices of an output tile that have been written; the CTA that draws the last ticket folds the
+  // slices in slice order and runs the epilogue, so nobody ever waits and the result does not depend
+  // on which CTA finishes last.  tickets must be zero at launch; the kernel leaves them zero.
+  int slices, k_tiles_per_slice;
+  T* partial;
+  unsigned int* tickets;
+};
+
+// One 16-byte shared-memory load into EV = 16 / sizeof(T) elements.
+__device__ __forceinline__ void lds16(uint32_t addr, float (&v)[4]) {
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lds16(uint32_t addr, uint32_t (&v)[4]) {
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lds16(uint32_t addr, int32_t (&v)[4]) {
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lds16(uint32_t addr, double (&v)[2]) {
+  asm volatile("ld.shared.v2.f64 {%0,%1}, [%2];" : "=d"(v[0]), "=d"(v[1]) : "r"(addr));
+}
+
+// Tile rasterisation: bands of kBand tile columns, rows fastest inside a band, so that the CTAs that
+// run at the same time share A row-panels and B column-panels in L2.
+constexpr int kBand = 16;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_band = kBand * tiles_m;
+  const int band = t / per_band;
+  const int in_band = t - band * per_band;
+  const int width = min(kBand, tiles_n - band * kBand);
+  tm = in_band / width;
+  tn = band * kBand + in_band % width;
+}
+
+template <typename RingT, bool kAK, bool kBK>
+__global__ void __launch_bounds__(kTmaThreads, 1)
+srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const TmaParams<typename RingT::Element> p) {
+  using T = typename RingT::Element;
+  constexpr int EV = 16 / sizeof(T);              // elements per 16-byte vector: 4 (fp32/int32) or 2 (fp64)
+  constexpr int TK = kTileKBytes / sizeof(T);     // k per stage: 32 or 16
+  constexpr int kChunks = TK / EV;                // 16-byte k chunks per stage: 8
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  unsigned int* ticket_smem = reinterpret_cast<unsigned int*>(empty_bar + kStages);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kConsumerWarps);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  const int k_tiles_total = (p.K + TK - 1) / TK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_work = num_tiles * p.slices;
+
+  if (warp >= kConsumerWarps) {
+    // ---------------------------------------------------------------- producer
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProducerRegs));
+    if (warp == kConsumerWarps && lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      uint32_t it = 0;  // running K-tile counter across all work items: stage = it % kStages
+      for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
+        const int z = w / num_tiles;
+        int tm, tn;
+        tile_coords(w - z * num_tiles, p.tiles_m, p.tiles_n, tm, tn);
+        const int kt_begin = z * p.k_tiles_per_slice;
+        const int kt_end = (z == p.slices - 1) ? k_tiles_total : min(k_tiles_total, kt_begin + p.k_tiles_per_slice);
+        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
+          const int s = it % kStages;
+          const uint32_t round = it / kStages;
+          if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1, p.status, kDeviceTimeoutEmpty)) return;
+          mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+          uint8_t* sa = smem + s * kStageBytes;
+          uint8_t* sb = sa + kOperandStageBytes;
+          if (kAK) tma_load_2d(sa, &map_a, &full_bar[s], kt * TK, tm * kTileM);
+          else     tma_load_2d(sa, &map_a, &full_bar[s], tm * kTileM, kt * TK);
+          if (kBK) tma_load_2d(sb, &map_b, &full_bar[s], kt * TK, tn * kTileN);
+          else     tma_load_2d(sb, &map_b, &full_bar[s], tn * kTileN, kt * TK);
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kConsumerRegs));
+  const int wm = warp / 4, wn = warp % 4;        // 2 x 4 warps
+  const int lr = lane / 4, lc = lane % 4;        // 8 x 4 lanes
+  // Row i (0..7) of this lane inside the warp's 64 rows; column j (0..7) inside the warp's 32 columns.
+  auto row_of = [&](int i) { return kAK ? (lr + 8 * i) : (EV * lr + (i % EV) + 8 * EV * (i / EV)); };
+  auto col_of = [&](int j) { return kBK ? (lc + 4 * j) : (EV * lc + (j % EV) + 4 * EV * (j / EV)); };
+
+  // Byte offset of this lane's first operand vector inside a stage; every other vector of the lane is a
+  // compile-time constant away from it.
+  //   K-contiguous:  row * 128 + ((chunk ^ (row & 7)) * 16)        (TMA 128-byte swizzle)
+  //                  A rows are lr + 8 i  -> + i * 1024 bytes, row & 7 == lr for every i
+  //                  B rows are lc + 4 j  -> + j * 512 bytes,  row & 7 == lc + 4 (j & 1)
+  //   MN-contiguous: k * (128 * sizeof(T)) + first_row_of_group * sizeof(T); groups are 8 EV (A) or
+  //                  4 EV (B) rows apart -> + g * 128 / + g * 64 bytes
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t a_base = kAK ? (wm * 64 + lr) * 128 : (wm * 64 + EV * lr) * (int)sizeof(T);
+  const uint32_t b_base = kBK ? (wn * 32 + lc) * 128 : (wn * 32 + EV * lc) * (int)sizeof(T);
+
+  T acc[8][8];
+
+  uint32_t it = 0;
+  for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
+    const int z = w / num_tiles;
+    int tm, tn;
+    tile_coords(w - z * num_tiles, p.tiles_m, p.tiles_n, tm, tn);
+    const int kt_begin = z * p.k_tiles_per_slice;
+    const int kt_end = (z == p.slices - 1) ? k_tiles_total : min(k_tiles_total, kt_begin + p.k_tiles_per_slice);
+
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = p.add_identity;
+
+    for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
+      const int s = it % kStages;
+      if (!mbar_wait(&full_bar[s], (it / kStages) & 1, p.status, kDeviceTimeoutFull)) return;
+      const uint32_t sa = smem_base + s * kStageBytes;
+      const uint32_t sb = sa + kOperandStageBytes;
+
+      // fragment loaders for one 16-byte k chunk: a[i][e] = A(row i, k = chunk * EV + e)
+      auto load_a = [&](T (&a)[8][EV], int chunk) {
+        if (kAK) {
+          const uint32_t base = sa + a_base + (((chunk ^ lr) & 7) << 4);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) lds16(base + i * 1024, a[i]);
+        } else {
+          const uint32_t base = sa + a_base + chunk * (EV * kTileM * (int)sizeof(T));
+#pragma unroll
+          for (int e = 0; e < EV; ++e) {
+#pragma unroll
+            for (int g = 0; g < 8 / EV; ++g) {
+              T v[EV];
+              lds16(base + e * (kTileM * (int)sizeof(T)) + g * 128, v);
+#pragma unroll
+              for (int t = 0; t < EV; ++t) a[g * EV + t][e] = v[t];
+            }
+          }
+        }
+      };
+      auto load_b = [&](T (&b)[8][EV], int chunk) {
+        if (kBK) {
+          const uint32_t base0 = sb + b_base + (((chunk ^ lc) & 7) << 4);
+          const uint32_t base1 = sb + b_base + (((chunk ^ (lc + 4)) & 7) << 4);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) lds16(((j & 1) ? base1 : base0) + j * 512, b[j]);
+        } else {
+          const uint32_t base = sb + b_base + chunk * (EV * kTileN * (int)sizeof(T));
+#pragma unroll
+          for (int e = 0; e < EV; ++e) {
+#pragma unroll
+            for (int g = 0; g < 8 / EV; ++g) {
+              T v[EV];
+              lds16(base + e * (kTileN * (int)sizeof(T)) + g * 64, v);
+#pragma unroll
+              for (int t = 0; t < EV; ++t) b[g * EV + t][e] = v[t];
+            }
+          }
+        }
+      };
+      auto compute = [&](const T (&a)[8][EV], const T (&b)[8][EV]) {
+#pragma unroll
+        for (int e = 0; e < EV; e += 2)
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              acc[i][j] = RingT::mac2(acc[i][j], a[i][e], b[j][e], a[i][e + 1], b[j][e + 1]);
+      };
+
+      T a0[8][EV], b0[8][EV], a1[8][EV], b1[8][EV];
+      load_a(a0, 0);
+      load_b(b0, 0);
+#pragma unroll 1
+      for (int chunk = 0; chunk < kChunks; chunk += 2) {
+        load_a(a1, chunk + 1);
+        load_b(b1, chunk + 1);
+        compute(a0, b0);
+        if (chunk + 2 < kChunks) {
+          load_a(a0, chunk + 2);
+          load_b(b0, chunk + 2);
+        } else {
+          // every load from this stage has been issued and, being volatile asm in program order with
+          // the uses below, has its data in registers before the math that follows retires; release it
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty_bar[s]);
+        }
+        compute(a1, b1);
+      }
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    const int m_base = tm * kTileM + wm * 64, n_base = tn * kTileN + wn * 32;
+    if (p.slices > 1) {
+      const int tile = w - z * num_tiles;
+      T* part = p.partial + (long long)z * p.M * p.N;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = m_base + row_of(i);
+        if (m >= p.M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int n = n_base + col_of(j);
+          if (n < p.N) part[(long long)m * p.N + n] = acc[i][j];
+        }
+      }
+      // publish this slice, then find out whether it completed the tile
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+      if (threadIdx.x == 0) *ticket_smem = atomicAdd(&p.tickets[tile], 1u);
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+      const bool last = (*ticket_smem == (unsigned)p.slices - 1);
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+      if (last) {
+        __threadfence();
+        if (threadIdx.x == 0) p.tickets[tile] = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = m_base + row_of(i);
+          if (m >= p.M) continue;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int n = n_base + col_of(j);
+            if (n >= p.N) continue;
+            T r = p.add_identity;
+            for (int zz = 0; zz < p.slices; ++zz)
+              r = RingT::add(__ldcg(p.partial + ((long long)zz * p.M + m) * p.N + n), r);
+            T v = RingT::mul(p.alpha, r);
+            if (p.read_c) v = RingT::add(v, RingT::mul(p.beta, p.C[(long long)m * p.ldc + n]));
+            p.D[(long long)m * p.ldd + n] = v;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = m_base + row_of(i);
+        if (m >= p.M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int n = n_base + col_of(j);
+          if (n >= p.N) continue;
+          T v = RingT::mul(p.alpha, acc[i][j]);
+          if (p.read_c) v = RingT::add(v, RingT::mul(p.beta, p.C[(long long)m * p.ldc + n]));
+          p.D[(long long)m * p.ldd + n] = v;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace cuasr_b200

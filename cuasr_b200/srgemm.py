@@ -1,0 +1,166 @@
+"""Host-side mirror of the reference's device-level operators, over the C ABI.
+
+`Srgemm` and `SrgemmSplitKParallel` keep the method names, argument meaning and status codes of
+cuasr::gemm::device::Srgemm (include/cuasr/gemm/device/srgemm.h:139-356) and
+cuasr::gemm::device::SrgemmSplitKParallel (include/cuasr/gemm/device/srgemm_splitk_parallel.h:155-378);
+template parameters become constructor arguments.  Matrices are device pointers with one leading
+dimension (cutlass::TensorRef); torch CUDA tensors are accepted wherever a pointer is.
+"""
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+from typing import Any, Optional, Tuple
+
+import numpy as np
+
+from . import _lib
+from .semiring import DType, Layout, NUMPY_DTYPE, Op, Status, annihilator, identity
+
+
+def _ptr(x: Any) -> Optional[int]:
+    if x is None:
+        return None
+    if hasattr(x, "data_ptr"):
+        return int(x.data_ptr())
+    return int(x)
+
+
+def _scalar(value, dtype: DType) -> _lib.Scalar:
+    s = _lib.Scalar()
+    raw = np.asarray(value).astype(NUMPY_DTYPE[dtype]).tobytes()
+    for i, b in enumerate(raw):
+        s.bytes[i] = b
+    return s
+
+
+def _stream_handle(stream) -> Optional[int]:
+    if stream is None:
+        return None
+    if hasattr(stream, "cuda_stream"):
+        return int(stream.cuda_stream)
+    return int(stream)
+
+
+@dataclasses.dataclass
+class Arguments:
+    """device::Srgemm::Arguments (device/srgemm.h:139-183)."""
+    problem_size: Tuple[int, int, int]                 # (M, N, K)
+    ref_A: Tuple[Any, int]                             # (pointer or tensor, leading dimension)
+    ref_B: Tuple[Any, int]
+    ref_C: Tuple[Any, int]
+    ref_D: Tuple[Any, int]
+    epilogue: Tuple[Any, ...] = ()                     # (), (alpha,), or (alpha, beta)
+    split_k_slices: int = 1
+
+
+class _Operator:
+    _splitk_parallel = False
+
+    def __init__(self, add_op: Op, mul_op: Op, dtype: DType = DType.F32,
+                 layout_a: Layout = Layout.COLUMN_MAJOR, layout_b: Layout = Layout.COLUMN_MAJOR,
+                 layout_c: Layout = Layout.COLUMN_MAJOR, split_k_serial: bool = False,
+                 add_identity=None, mul_identity=None):
+        self.add_op, self.mul_op, self.dtype = Op(add_op), Op(mul_op), DType(dtype)
+        self.layout_a, self.layout_b, self.layout_c = Layout(layout_a), Layout(layout_b), Layout(layout_c)
+        self.kSplitKSerial = bool(split_k_serial)
+        # AdditionOp::Identity / MultiplicationOp::Identity of the functors the operator is "instantiated" with
+        self.add_identity = identity(self.add_op, self.dtype) if add_identity is None else add_identity
+        self.mul_identity = identity(self.mul_op, self.dtype) if mul_identity is None else mul_identity
+        self._lib = _lib.load()
+        self._desc = _lib.Desc(int(self.add_op), int(self.mul_op), int(self.dtype), int(self.layout_a),
+                               int(self.layout_b), int(self.layout_c), int(self.kSplitKSerial), 0)
+        self._args: Optional[_lib.Args] = None
+        self._keepalive = None
+
+    # -- helpers ---------------------------------------------------------------------------------------
+    def _pack(self, args: Arguments, workspace=None, workspace_bytes: int = 0, stream=None) -> _lib.Args:
+        m, n, k = args.problem_size
+        epi = tuple(args.epilogue)
+        # EpilogueOutputOp::Params defaults (semiring_linear_combination.h:67-85)
+        alpha = epi[0] if len(epi) >= 1 else self.mul_identity
+        beta = epi[1] if len(epi) >= 2 else annihilator(self.mul_op, self.dtype)
+        a = _lib.Args()
+        a.m, a.n, a.k, a.split_k_slices = int(m), int(n), int(k), int(args.split_k_slices)
+        a.A, a.lda = _ptr(args.ref_A[0]), int(args.ref_A[1])
+        a.B, a.ldb = _ptr(args.ref_B[0]), int(args.ref_B[1])
+        a.C, a.ldc = _ptr(args.ref_C[0]), int(args.ref_C[1])
+        a.D, a.ldd = _ptr(args.ref_D[0]), int(args.ref_D[1])
+        a.alpha, a.beta = _scalar(alpha, self.dtype), _scalar(beta, self.dtype)
+        a.add_identity = _scalar(self.add_identity, self.dtype)
+        a.mul_identity = _scalar(self.mul_identity, self.dtype)
+        a.workspace = _ptr(workspace)
+        if workspace is not None and workspace_bytes == 0 and hasattr(workspace, "numel"):
+            workspace_bytes = workspace.numel() * workspace.element_size()
+        a.workspace_bytes = int(workspace_bytes)
+        a.stream = _stream_handle(stream)
+        return a
+
+    def _fn(self, base: str):
+        name = "cuasr_b200_srgemm_splitk" if self._splitk_parallel else "cuasr_b200_srgemm"
+        return getattr(self._lib, name + base)
+
+    # -- the reference's interface -----------------------------------------------------------------------
+    def can_implement(self, args: Arguments) -> Status:
+        return Status(self._fn("_can_implement")(ctypes.byref(self._desc), ctypes.byref(self._pack(args))))
+
+    def get_workspace_size(self, args: Arguments) -> int:
+        return int(self._fn("_workspace_size")(ctypes.byref(self._desc), ctypes.byref(self._pack(args))))
+
+    def initialize(self, args: Arguments, workspace=None, stream=None, workspace_bytes: int = 0) -> Status:
+        packed = self._pack(args, workspace, workspace_bytes, stream)
+        status = Status(self._fn("_can_implement")(ctypes.byref(self._desc), ctypes.byref(packed)))
+        if status != Status.kSuccess:
+            return status
+        need = self._fn("_workspace_size")(ctypes.byref(self._desc), ctypes.byref(packed))
+        if need > 0 and packed.workspace is None:
+            return Status.kErrorWorkspaceNull
+        self._args = packed
+        self._keepalive = (args, workspace)
+        return Status.kSuccess
+
+    def update(self, args: Arguments, workspace=None, workspace_bytes: int = 0) -> Status:
+        """Refreshes pointers only (device/srgemm.h:285-300)."""
+        if self._args is None:
+            return Status.kErrorInternal
+        stream = self._args.stream
+        self._args = self._pack(args, workspace, workspace_bytes, stream)
+        self._keepalive = (args, workspace)
+        return Status.kSuccess
+
+    def run(self, stream=None) -> Status:
+        if self._args is None:
+            return Status.kErrorInternal
+        if stream is not None:
+            self._args.stream = _stream_handle(stream)
+        return Status(self._fn("")(ctypes.byref(self._desc), ctypes.byref(self._args)))
+
+    def __call__(self, args: Optional[Arguments] = None, workspace=None, stream=None,
+                 workspace_bytes: int = 0) -> Status:
+        if args is not None:
+            status = self.initialize(args, workspace, stream, workspace_bytes)
+            if status != Status.kSuccess:
+                return status
+        return self.run(stream)
+
+    # -- extras ------------------------------------------------------------------------------------------
+    def last_kernel(self) -> str:
+        return self._lib.cuasr_b200_last_kernel().decode()
+
+
+class Srgemm(_Operator):
+    """cuasr::gemm::device::Srgemm."""
+
+
+class SrgemmSplitKParallel(_Operator):
+    """cuasr::gemm::device::SrgemmSplitKParallel."""
+    _splitk_parallel = True
+
+
+def device_status(stream=None) -> int:
+    """Synchronises `stream` and returns the device-side status word (0 = ok)."""
+    return int(_lib.load().cuasr_b200_device_status(_stream_handle(stream)))
+
+
+def launch_count() -> int:
+    return int(_lib.load().cuasr_b200_launch_count())

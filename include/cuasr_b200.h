@@ -1,0 +1,111 @@
+/*
+ * C ABI of the B200 (sm_100a) semiring-GEMM library.
+ *
+ * These entry points are what a binding of the reference's device-level API
+ *   cuasr::gemm::device::Srgemm               (include/cuasr/gemm/device/srgemm.h:85-357, :398-567)
+ *   cuasr::gemm::device::SrgemmSplitKParallel (include/cuasr/gemm/device/srgemm_splitk_parallel.h:101-378, :424-607)
+ * calls: the template parameters of those classes travel in a descriptor (operator codes, element type,
+ * layouts), their `Arguments` in an argument block.  All pointers are DEVICE pointers owned by the
+ * caller; nothing here allocates, frees or synchronises with the host (the reference keeps only a
+ * Params copy: device/srgemm.h:188), and every launch is asynchronous on the given stream.
+ * Return values use cutlass::Status numbering (cuasr_status_t), 0 = success.
+ *
+ * The header-only C++ facade in include/cuasr/ turns `Srgemm<AdditionOp, MultiplicationOp, ...>` objects
+ * into calls of these functions.
+ */
+#ifndef CUASR_B200_H
+#define CUASR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "cuasr_b200_types.h"
+
+#if defined(__GNUC__)
+#define CUASR_B200_API __attribute__((visibility("default")))
+#else
+#define CUASR_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* The compile-time half of the reference's interface: template parameters of device::Srgemm
+ * (device/srgemm.h:28-84).  Element type is one type for A, B, C, D, accumulator and scalars. */
+typedef struct cuasr_b200_desc {
+  int32_t add_op;    /* cuasr_op_t: AdditionOp        */
+  int32_t mul_op;    /* cuasr_op_t: MultiplicationOp  */
+  int32_t dtype;     /* cuasr_dtype_t                 */
+  int32_t layout_a;  /* cuasr_layout_t of A (M x K)   */
+  int32_t layout_b;  /* cuasr_layout_t of B (K x N)   */
+  int32_t layout_c;  /* cuasr_layout_t of C and D (M x N) */
+  /* kSplitKSerial of device::Srgemm (device/srgemm.h:83, :198-200): when 0, split_k_slices > 1 is an
+   * invalid problem for cuasr_b200_srgemm; when 1, the K range is split and combined inside one launch. */
+  int32_t split_k_serial;
+  int32_t reserved;
+} cuasr_b200_desc_t;
+
+/* One element of the descriptor's dtype, stored in the first sizeof(element) bytes. */
+typedef struct cuasr_b200_scalar {
+  unsigned char bytes[8];
+} cuasr_b200_scalar_t;
+
+/* The run-time half: device::Srgemm::Arguments (device/srgemm.h:139-183) plus the workspace and stream
+ * that initialize()/run() take (device/srgemm.h:237, :303).  Leading dimensions are in elements. */
+typedef struct cuasr_b200_args {
+  int32_t m, n, k;                  /* GemmCoord problem_size */
+  int32_t split_k_slices;           /* Arguments::split_k_slices, default 1 */
+  const void *A; int64_t lda;       /* ref_A */
+  const void *B; int64_t ldb;       /* ref_B */
+  const void *C; int64_t ldc;       /* ref_C; may be NULL when the epilogue does not need the source */
+  void *D;       int64_t ldd;       /* ref_D; may alias C */
+  cuasr_b200_scalar_t alpha;        /* EpilogueOutputOp::Params::alpha (semiring_linear_combination.h:54-100) */
+  cuasr_b200_scalar_t beta;         /* EpilogueOutputOp::Params::beta  */
+  cuasr_b200_scalar_t add_identity; /* AdditionOp::Identity of the caller's functor: start value of every
+                                       accumulator (kernel/srgemm.h:220-221) */
+  cuasr_b200_scalar_t mul_identity; /* MultiplicationOp::Identity: used only to decide whether C is read
+                                       (semiring_linear_combination.h:118-125) */
+  void *workspace;                  /* device scratch of at least cuasr_b200_*_workspace_size bytes, or NULL */
+  size_t workspace_bytes;
+  void *stream;                     /* cudaStream_t */
+} cuasr_b200_args_t;
+
+/* Srgemm::can_implement (device/srgemm.h:196-215): validates sizes, pointers and the split-K setting. */
+CUASR_B200_API int cuasr_b200_srgemm_can_implement(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
+
+/* Srgemm::get_workspace_size (device/srgemm.h:218-234): bytes of device scratch the call needs
+ * (0 unless desc->split_k_serial and split_k_slices > 1). */
+CUASR_B200_API size_t cuasr_b200_srgemm_workspace_size(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
+
+/* Srgemm::operator()(args, workspace, stream) = initialize + run (device/srgemm.h:237-336, :344-356):
+ * enqueues D = add(mul(alpha, A (x)(+) B), mul(beta, C)) and returns without waiting. */
+CUASR_B200_API int cuasr_b200_srgemm(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
+
+/* SrgemmSplitKParallel::can_implement / get_workspace_size / operator()
+ * (device/srgemm_splitk_parallel.h:220-235, :238-279, :333-348).  The reference needs
+ * sizeof(element) * M * N * slices bytes of workspace and two launches; this library needs a little more
+ * (per-tile arrival counters) and one launch: the CTA that completes a tile last combines the slices
+ * in slice order and applies the epilogue. */
+CUASR_B200_API int cuasr_b200_srgemm_splitk_can_implement(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
+CUASR_B200_API size_t cuasr_b200_srgemm_splitk_workspace_size(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
+CUASR_B200_API int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
+
+/* Reads (and clears) the device-side status word of the current device after synchronising `stream`:
+ * 0 = every kernel of this library ran to completion; otherwise a bounded wait inside a kernel expired
+ * (1: tile never arrived, 2: stage never released, 3: peer flag never set).  This call blocks. */
+CUASR_B200_API int cuasr_b200_device_status(void *stream);
+
+/* Name of the kernel the last cuasr_b200_srgemm* call on this thread launched ("tma", "generic", ...). */
+CUASR_B200_API const char *cuasr_b200_last_kernel(void);
+
+/* Number of kernels this library has launched in this process so far. */
+CUASR_B200_API uint64_t cuasr_b200_launch_count(void);
+
+CUASR_B200_API const char *cuasr_b200_status_string(int status);
+CUASR_B200_API const char *cuasr_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUASR_B200_H */

@@ -1,0 +1,74 @@
+"""ctypes loaders of the two CPU checkers.  TEST INFRASTRUCTURE: import only from tests/, from the smoke
+check and from the CPU-baseline leg of bench.py.
+
+`srgemm(...)`     -> oracle/libcuasr_oracle.so, the plain-C restatement (srgemm_oracle.c)
+`ref_srgemm(...)` -> oracle/_ref/libcuasr_ref.so, the reference's own host_srgemm.h compiled unmodified
+                     (ref_host_srgemm.cpp); present only where it was built.
+Both take numpy arrays (any strides are NOT honoured: pass the buffer and its leading dimension).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_PATH = os.path.join(_HERE, "libcuasr_oracle.so")
+REF_PATH = os.path.join(_HERE, "_ref", "libcuasr_ref.so")
+
+_ARGTYPES = [ctypes.c_int] * 9 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                  ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                  ctypes.c_void_p, ctypes.c_int]
+_libs = {}
+
+
+def _load(path: str, symbol: str):
+    if path not in _libs:
+        lib = ctypes.CDLL(path)
+        fn = getattr(lib, symbol)
+        fn.restype = ctypes.c_int
+        fn.argtypes = _ARGTYPES
+        _libs[path] = (lib, fn)
+    return _libs[path]
+
+
+def have_ref() -> bool:
+    return os.path.exists(REF_PATH)
+
+
+def max_threads(ref: bool = False) -> int:
+    lib, _ = _load(REF_PATH, "cuasr_ref_srgemm") if ref else _load(ORACLE_PATH, "cuasr_oracle_srgemm")
+    fn = lib.cuasr_ref_max_threads if ref else lib.cuasr_oracle_max_threads
+    fn.restype = ctypes.c_int
+    return int(fn())
+
+
+def _call(fn, add_op, mul_op, dtype, layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, add_identity,
+          nthreads):
+    np_t = D.dtype.type
+    for arr in (A, B, C, D):
+        assert arr.dtype == D.dtype and arr.flags["C_CONTIGUOUS"]
+    al, be, ident = (np.array([v], dtype=np_t) for v in (alpha, beta, add_identity))
+    st = fn(int(add_op), int(mul_op), int(dtype), int(layouts[0]), int(layouts[1]), int(layouts[2]),
+            int(mnk[0]), int(mnk[1]), int(mnk[2]), al.ctypes.data, A.ctypes.data, int(lda), B.ctypes.data, int(ldb),
+            be.ctypes.data, C.ctypes.data, int(ldc), D.ctypes.data, int(ldd), ident.ctypes.data, int(nthreads))
+    if st != 0:
+        raise RuntimeError(f"oracle returned status {st}")
+    return D
+
+
+def srgemm(add_op, mul_op, dtype, layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, add_identity,
+           nthreads: int = 0):
+    """D = add(mul(alpha, A (x)(+) B), mul(beta, C)) with the C restatement; fills and returns D."""
+    _, fn = _load(ORACLE_PATH, "cuasr_oracle_srgemm")
+    return _call(fn, add_op, mul_op, dtype, layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd,
+                 add_identity, nthreads)
+
+
+def ref_srgemm(add_op, mul_op, dtype, layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, add_identity,
+               nthreads: int = 0):
+    """Same call on the reference's own host SRGEMM (only where oracle/_ref has been built)."""
+    _, fn = _load(REF_PATH, "cuasr_ref_srgemm")
+    return _call(fn, add_op, mul_op, dtype, layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd,
+                 add_identity, nthreads)

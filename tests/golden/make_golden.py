@@ -1,0 +1,76 @@
+"""Generates the golden fixtures of tests/golden/ from the REFERENCE checkout.  Run in a container that has
+the reference (default /root/reference) and oracle/_ref built (`make -C oracle ref`):
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+Writes
+  regress_known_answer.json   the hand-written 4x4x2 min-plus case of test/regress/Srgemm_test.cu:15-62,
+                              parsed from the reference's test source
+  host_srgemm_outputs.npz     outputs of the reference's own host_srgemm.h (oracle/_ref) for every ring,
+                              element type and layout combination on seeded small-integer inputs, with the
+                              inputs, so that the fixtures do not depend on any random generator
+"""
+import json
+import os
+import re
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import oracle  # noqa: E402
+import util  # noqa: E402
+from cuasr_b200 import DType, Layout  # noqa: E402
+
+
+def known_answer(reference):
+    src = open(os.path.join(reference, "test", "regress", "Srgemm_test.cu")).read()
+    body = src[src.index("CpuNaiveCorrect"):src.index("cpu_srgemm_naive(")]
+    mats = re.findall(r"Matrix<float>\(\s*(\d+),\s*(\d+),\s*\{(.*?)\}\)", body, flags=re.S)
+    names = ["a", "b", "c", "correct"]
+    out = {"source": "test/regress/Srgemm_test.cu:15-62", "layout": "column-major", "semiring": "min-plus",
+           "epilogue": "C = min(C, A (x) B)"}
+    for name, (rows, cols, vals) in zip(names, mats):
+        nums = [float(v) for v in re.findall(r"[-+]?\d*\.\d+|\d+", re.sub(r"//.*", "", vals))]
+        assert len(nums) == int(rows) * int(cols), (name, len(nums))
+        out[name] = {"rows": int(rows), "cols": int(cols), "data": nums}
+    return out
+
+
+def host_outputs():
+    rng = np.random.default_rng(2080)
+    store = {}
+    shapes = [(13, 11, 9)]
+    for ring, dt in util.ring_dtype_cases():
+        for li, layouts in enumerate(util.ALL_LAYOUTS):
+            for (m, n, k) in shapes + ([(65, 33, 47)] if li == 0 else []):
+                A, lda = util.make_matrix(rng, dt, layouts[0], m, k)
+                B, ldb = util.make_matrix(rng, dt, layouts[1], k, n)
+                C, ldc = util.make_matrix(rng, dt, layouts[2], m, n)
+                alpha, beta = util.default_scalars(ring, dt)
+                key = f"{ring}|{int(dt)}|{''.join(str(int(x)) for x in layouts)}|{m}x{n}x{k}"
+                # inputs are integers in [-8, 8]: stored as int8, cast back to the element type on load
+                store[key + "|A"], store[key + "|B"], store[key + "|C"] = (x.astype(np.int8) for x in (A, B, C))
+                # beta = mult annihilator (TestAllGemm) and beta = mult identity (the source matrix takes part)
+                for tag, be in (("ann", beta), ("id", alpha)):
+                    D = util.run_oracle(ring, dt, layouts, (m, n, k), alpha, A, lda, B, ldb, be, C, ldc, use_ref=True)
+                    store[key + "|D" + tag] = D
+    return store
+
+
+def main():
+    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref"
+    with open(os.path.join(HERE, "regress_known_answer.json"), "w") as f:
+        json.dump(known_answer(reference), f, indent=1)
+    store = host_outputs()
+    np.savez_compressed(os.path.join(HERE, "host_srgemm_outputs.npz"), **store)
+    print(len(store) // 5, "input sets written")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,224 @@
+"""Parity of the CUDA library (through the C ABI) with the CPU oracle.  Bit-exact (value equality, like
+cutlass TensorEquals) for every ring except plus-times on non-integer data, which gets a stated tolerance."""
+import numpy as np
+import pytest
+
+import golden_io
+import util
+from cuasr_b200 import (Arguments, DType, Layout, Op, RINGS, Srgemm, SrgemmSplitKParallel, Status, annihilator,
+                        device_status, identity)
+from cuasr_b200.semiring import NUMPY_DTYPE
+
+pytestmark = pytest.mark.gpu
+COL, ROW = Layout.COLUMN_MAJOR, Layout.ROW_MAJOR
+
+
+def _check(ring, dt, layouts, mnk, rng, pad=0, beta_is_identity=False, expect_kernel=None, **kw):
+    m, n, k = mnk
+    A, lda = util.make_matrix(rng, dt, layouts[0], m, k, util.extents(layouts[0], m, k)[0] + pad)
+    B, ldb = util.make_matrix(rng, dt, layouts[1], k, n, util.extents(layouts[1], k, n)[0] + pad)
+    C, ldc = util.make_matrix(rng, dt, layouts[2], m, n, util.extents(layouts[2], m, n)[0] + pad)
+    alpha, beta = util.default_scalars(ring, dt)
+    if beta_is_identity:
+        beta = alpha
+    canary = np.full_like(C, 77)
+    want = util.run_oracle(ring, dt, layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D_init=canary)
+    got, kernel = util.run_device(ring, dt, layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D_init=canary, **kw)
+    what = f"{ring} {dt.name} {[int(x) for x in layouts]} {mnk} pad={pad} kernel={kernel}"
+    util.assert_equal(got, want, layouts[2], m, n, ldc, what=what)
+    # nothing outside the logical matrix may be written (the padding of each line keeps its canary)
+    assert np.array_equal(got, want), f"{what}: bytes outside the matrix were modified"
+    if expect_kernel is not None:
+        assert kernel == expect_kernel, what
+    return kernel
+
+
+@pytest.mark.parametrize("ring,dt", list(util.ring_dtype_cases()))
+def test_reference_grid(cuda_device, ring, dt):
+    """TestAllGemm's grid (test/device/testbed.h:313-358): M in {1, 509}, N in {1, 510}, K in {1, 23}, all eight
+    layout combinations, alpha = mult identity, beta = mult annihilator, integers in [-8, 8]."""
+    rng = np.random.default_rng(2080)
+    for layouts in util.ALL_LAYOUTS:
+        for m in (1, 509):
+            for n in (1, 510):
+                for k in (1, 23):
+                    _check(ring, dt, layouts, (m, n, k), rng)
+    assert device_status() == 0
+
+
+@pytest.mark.parametrize("ring,dt", [(r, d) for r, d in util.ring_dtype_cases() if d in (DType.F32, DType.U32)])
+def test_tma_kernel_ragged_but_aligned(cuda_device, ring, dt):
+    """16-byte aligned operands take the TMA kernel; M, N, K tails are not multiples of the tile."""
+    from cuasr_b200.srgemm import _lib
+    rng = np.random.default_rng(99)
+    kernels = set()
+    for layouts in util.ALL_LAYOUTS:
+        for mnk in ((260, 392, 100), (128, 128, 32), (132, 516, 36)):
+            for beta_id in (False, True):
+                kernels.add(_check(ring, dt, layouts, mnk, rng, beta_is_identity=beta_id))
+    assert device_status() == 0
+    fast = {"minimum_plus", "maximum_plus", "minimum_maximum", "maximum_minimum", "plus_multiplies",
+            "minimum_multiplies", "maximum_multiplies"}
+    if dt == DType.F32 and ring in fast:
+        assert kernels == {"tma"}, kernels
+    if dt == DType.U32 and ring in ("bit_xor_bit_and", "bit_or_bit_and", "bit_xor_binary_and"):
+        assert kernels == {"tma"}, kernels
+
+
+def test_config_minplus_f32_512_cube(cuda_device):
+    """Min-plus fp32, M = N = K = 512, column-major, A and B uniform in [0, 100), C filled with the additive
+    identity, alpha = beta = 0 (the multiplicative identity of min-plus): bit-exact."""
+    rng = np.random.default_rng(3090)
+    n = 512
+    A = (rng.random(n * n, dtype=np.float32) * 100).astype(np.float32)
+    B = (rng.random(n * n, dtype=np.float32) * 100).astype(np.float32)
+    ident = identity(Op.MINIMUM, DType.F32)
+    C = np.full(n * n, ident, np.float32)
+    layouts = (COL, COL, COL)
+    want = util.run_oracle("minimum_plus", DType.F32, layouts, (n, n, n), 0.0, A, n, B, n, 0.0, C, n)
+    got, kernel = util.run_device("minimum_plus", DType.F32, layouts, (n, n, n), 0.0, A, n, B, n, 0.0, C, n)
+    assert kernel == "tma"
+    assert np.array_equal(got, want)
+    # with true infinities as identity and fill the finite entries are the same
+    inf = np.float32(np.inf)
+    got2, _ = util.run_device("minimum_plus", DType.F32, layouts, (n, n, n), 0.0, A, n, B, n, 0.0,
+                              np.full(n * n, inf, np.float32), n, add_identity=inf)
+    assert np.array_equal(got2, want)
+    assert device_status() == 0
+
+
+def test_known_answer_on_device(cuda_device):
+    """test/regress/Srgemm_test.cu:64-116 (the GPU twin of the CPU known-answer test)."""
+    ka = golden_io.known_answer()
+    a, b, c, want = (np.array(ka[k]["data"], dtype=np.float32) for k in ("a", "b", "c", "correct"))
+    got, _ = util.run_device("minimum_plus", DType.F32, (COL, COL, COL), (4, 4, 2), 0.0, a, 4, b, 2, 0.0, c, 4)
+    assert np.all(np.abs(got - want) <= 4 * np.spacing(np.abs(want)))
+
+
+def test_committed_reference_outputs_on_device(cuda_device):
+    """The fixtures under tests/golden/ were produced by the reference's own host SRGEMM."""
+    count = 0
+    for case in golden_io.host_cases():
+        ring, dt, layouts, (m, n, k) = case["ring"], case["dtype"], case["layouts"], case["mnk"]
+        lda, ldb, ldc = (util.extents(layouts[0], m, k)[0], util.extents(layouts[1], k, n)[0],
+                         util.extents(layouts[2], m, n)[0])
+        alpha, beta = util.default_scalars(ring, dt)
+        for tag, be in (("D_ann", beta), ("D_id", alpha)):
+            got, _ = util.run_device(ring, dt, layouts, (m, n, k), alpha, case["A"], lda, case["B"], ldb, be,
+                                     case["C"], ldc)
+            util.assert_equal(got, case[tag], layouts[2], m, n, ldc, what=f"{case['key']} {tag}")
+            count += 1
+    assert count >= 600
+    assert device_status() == 0
+
+
+@pytest.mark.parametrize("ring", ["minimum_plus", "maximum_minimum", "plus_multiplies"])
+def test_submatrix_views(cuda_device, ring):
+    """Operands that are windows of larger matrices: ld > extent and offset base pointers, as in
+    test/regress/Srgemm_test.cu:253-537 (top-left / bottom-right sub-blocks) and :539-605 (odd shapes)."""
+    import torch
+    rng = np.random.default_rng(5)
+    dt = DType.F32
+    big = 160
+    for (m, n, k, off) in ((64, 64, 64, 0), (64, 64, 64, 96), (17, 27, 17, 0), (7, 6, 5, 3), (128, 128, 8, 32)):
+        for layouts in (util.ALL_LAYOUTS[0], util.ALL_LAYOUTS[2], util.ALL_LAYOUTS[7]):
+            A, _ = util.make_matrix(rng, dt, COL, big, big)
+            B, _ = util.make_matrix(rng, dt, COL, big, big)
+            C, _ = util.make_matrix(rng, dt, COL, big, big)
+            start = off * big + off  # element (off, off) of a big x big matrix in either layout
+            alpha, beta = util.default_scalars(ring, dt)
+            beta = alpha
+            want = util.run_oracle(ring, dt, layouts, (m, n, k), alpha, A[start:], big, B[start:], big, beta,
+                                   C[start:], big, D_init=C[start:].copy())
+            dA, dB, dC = (torch.from_numpy(x).cuda() for x in (A, B, C))
+            op = Srgemm(*RINGS[ring], dt, *layouts)
+            es = 4
+            args = Arguments((m, n, k), (dA.data_ptr() + start * es, big), (dB.data_ptr() + start * es, big),
+                             (dC.data_ptr() + start * es, big), (dC.data_ptr() + start * es, big), (alpha, beta))
+            assert op(args) == Status.kSuccess  # C aliases D, like examples/00_minplus_srgemm/minplus_srgemm.cu:67-81
+            torch.cuda.synchronize()
+            got = dC.cpu().numpy()
+            assert np.array_equal(got[start:], want), (ring, m, n, k, off, layouts)
+            assert np.array_equal(got[:start], C[:start])
+    assert device_status() == 0
+
+
+@pytest.mark.parametrize("ring,dt", [("minimum_plus", DType.F32), ("plus_multiplies", DType.F32),
+                                     ("maximum_plus", DType.F64), ("bit_xor_bit_and", DType.U32),
+                                     ("minimum_plus", DType.S32)])
+def test_split_k_equals_single_pass(cuda_device, ring, dt):
+    """Parallel split-K equals the single-pass result exactly (examples/02_splitk_srgemm/splitk_srgemm.cu:270-287)
+    and the oracle; also through the kSplitKSerial flag of Srgemm."""
+    rng = np.random.default_rng(17)
+    layouts = (ROW, COL, ROW)  # the layout of examples/02: A row-major, B column-major, C row-major
+    for (m, n, k) in ((256, 256, 4096), (130, 70, 1000)):
+        A, lda = util.make_matrix(rng, dt, layouts[0], m, k)
+        B, ldb = util.make_matrix(rng, dt, layouts[1], k, n)
+        C, ldc = util.make_matrix(rng, dt, layouts[2], m, n)
+        alpha, _ = util.default_scalars(ring, dt)
+        beta = alpha
+        want = util.run_oracle(ring, dt, layouts, (m, n, k), alpha, A, lda, B, ldb, beta, C, ldc)
+        single, _ = util.run_device(ring, dt, layouts, (m, n, k), alpha, A, lda, B, ldb, beta, C, ldc)
+        assert np.array_equal(single, want)
+        for slices in (2, 3, 16):
+            got, kernel = util.run_device(ring, dt, layouts, (m, n, k), alpha, A, lda, B, ldb, beta, C, ldc,
+                                          split_k_slices=slices, parallel_splitk=True)
+            assert np.array_equal(got, single), (ring, slices, kernel)
+            got, kernel = util.run_device(ring, dt, layouts, (m, n, k), alpha, A, lda, B, ldb, beta, C, ldc,
+                                          split_k_slices=slices, split_k_serial=True)
+            assert np.array_equal(got, single), (ring, slices, kernel)
+    assert device_status() == 0
+
+
+def test_plus_times_tolerance(cuda_device):
+    """Plus-times on non-integer data: the device fuses multiply-add and sums in a different order, so the
+    check is |got - want| <= 8 K eps (|A| |B|)_ij."""
+    rng = np.random.default_rng(23)
+    for dt, eps in ((DType.F32, 2.0 ** -24), (DType.F64, 2.0 ** -53)):
+        np_t = NUMPY_DTYPE[dt]
+        m, n, k = 256, 192, 520
+        A = (rng.random(m * k) * 2 - 1).astype(np_t)
+        B = (rng.random(k * n) * 2 - 1).astype(np_t)
+        C = np.zeros(m * n, np_t)
+        layouts = (COL, COL, COL)
+        want = util.run_oracle("plus_multiplies", dt, layouts, (m, n, k), 1.0, A, m, B, k, 0.0, C, m)
+        got, _ = util.run_device("plus_multiplies", dt, layouts, (m, n, k), 1.0, A, m, B, k, 0.0, C, m)
+        bound = 8 * k * eps * (np.abs(A.reshape(k, m).T.astype(np.float64)) @ np.abs(B.reshape(n, k).T.astype(np.float64)))
+        err = np.abs(got.reshape(n, m).T.astype(np.float64) - want.reshape(n, m).T.astype(np.float64))
+        assert np.all(err <= bound)
+
+
+def test_status_codes(cuda_device):
+    """Error behaviour of device::Srgemm (device/srgemm.h:196-266) and SrgemmSplitKParallel (:247-249)."""
+    import torch
+    x = torch.zeros(64 * 64, device="cuda")
+    ok = Arguments((64, 64, 64), (x, 64), (x, 64), (x, 64), (x, 64), (0.0, 0.0))
+    op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL)
+    assert op.can_implement(ok) == Status.kSuccess
+    assert op.get_workspace_size(ok) == 0
+    # split-K on an operator that was not built with kSplitKSerial
+    bad = Arguments((64, 64, 64), (x, 64), (x, 64), (x, 64), (x, 64), (0.0, 0.0), split_k_slices=2)
+    assert op.can_implement(bad) == Status.kErrorInvalidProblem
+    assert op(bad) == Status.kErrorInvalidProblem
+    # serial split-K wants a workspace
+    ser = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL, split_k_serial=True)
+    assert ser.get_workspace_size(bad) > 0
+    assert ser(bad, None) == Status.kErrorWorkspaceNull
+    par = SrgemmSplitKParallel(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL)
+    assert par.get_workspace_size(bad) >= 4 * 64 * 64 * 2
+    assert par(bad, None) == Status.kErrorWorkspaceNull
+    # empty problem, short leading dimension, misaligned pointer, unsupported ring
+    assert op.can_implement(Arguments((0, 64, 64), (x, 64), (x, 64), (x, 64), (x, 64))) == Status.kErrorInvalidProblem
+    assert op.can_implement(Arguments((64, 64, 64), (x, 32), (x, 64), (x, 64), (x, 64))) == Status.kErrorInvalidProblem
+    assert op.can_implement(Arguments((8, 8, 8), (x.data_ptr() + 2, 64), (x, 64), (x, 64), (x, 64))) \
+        == Status.kErrorMisalignedOperand
+    weird = Srgemm(Op.BIT_XOR, Op.BIT_AND, DType.F32, COL, COL, COL)
+    assert weird.can_implement(ok) == Status.kErrorNotSupported
+    # the default epilogue (alpha = mult identity, beta = mult annihilator) does not read C: C may be null
+    noc = Arguments((64, 64, 64), (x, 64), (x, 64), (None, 64), (x, 64))
+    assert op(noc) == Status.kSuccess
+    torch.cuda.synchronize()
+    # ... but a beta that needs the source does
+    needs = Arguments((64, 64, 64), (x, 64), (x, 64), (None, 64), (x, 64), (0.0, 0.0))
+    assert op(needs) == Status.kErrorInvalidProblem
+    assert device_status() == 0
