@@ -108,6 +108,14 @@ def default_scalars(ring, dtype):
     return identity(mul_op, dtype), annihilator(mul_op, dtype)
 
 
+def annihilator_beta_is_defined(ring, dtype):
+    """False where beta = mult annihilator makes the host SRGEMM's `mult(beta, C)` overflow: for integer element
+    types the annihilator of `plus` is numeric_limits::max() (functional.h:42), max() + C wraps (undefined for
+    signed), and the device epilogue does not even read C then (semiring_linear_combination.h:118-125).  The
+    reference only tests float and double (test/device/simt_sm50.py:27-33); integer cases use beta = identity."""
+    return not (dtype in (DType.S32, DType.U32) and RINGS[ring][1] == Op.PLUS)
+
+
 def assert_equal(got, want, layout, m, n, ld, what=""):
     """Value equality on the logical matrix, like cutlass TensorEquals (test/device/testbed.h:159-160)."""
     g, w = as_2d(got, layout, m, n, ld), as_2d(want, layout, m, n, ld)
