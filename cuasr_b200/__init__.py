@@ -5,4 +5,5 @@ include/cuasr/.  This Python package is the harness side: a ctypes binding and a
 reference's `Srgemm` / `SrgemmSplitKParallel` host operators used by the tests and the benchmark.
 """
 from .semiring import DType, Layout, Op, RINGS, Status, annihilator, identity  # noqa: F401
-from .srgemm import Arguments, Srgemm, SrgemmSplitKParallel, device_status, launch_count  # noqa: F401
+from .srgemm import (Arguments, Srgemm, SrgemmSplitKParallel, STATIC_SCRATCH_BYTES, device_status,  # noqa: F401
+                     launch_count, srgemm_splitk_static)

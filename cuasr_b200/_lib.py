@@ -44,6 +44,7 @@ PROTOTYPES = {
     "cuasr_b200_srgemm_splitk_can_implement": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_splitk_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_splitk": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
+    "cuasr_b200_srgemm_splitk_static": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_device_status": (ctypes.c_int, [ctypes.c_void_p]),
     "cuasr_b200_last_kernel": (ctypes.c_char_p, []),
     "cuasr_b200_launch_count": (ctypes.c_uint64, []),

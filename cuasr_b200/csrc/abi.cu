@@ -337,6 +337,30 @@ int run(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args, int slices
   }
 }
 
+// ---- built-in scratch for cuasr_b200_srgemm_splitk_static --------------------------------------------
+// The array is device memory that belongs to the loaded module.  Its name is only a host-side handle: a
+// kernel must be given the address cudaGetSymbolAddress returns for the CURRENT device, never the name.
+static __device__ __align__(256) unsigned char g_static_scratch[CUASR_B200_STATIC_SCRATCH_BYTES];
+void* g_static_scratch_ptr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the static scratch on the current device; looked up once per device.
+cudaError_t static_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (err != cudaSuccess) return err;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return cudaSuccess;
+}
+
 }  // namespace
 }  // namespace cuasr_b200
 
@@ -381,6 +405,19 @@ int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t* desc, const cuasr_b200_arg
   return run(desc, args, args->split_k_slices);
 }
 
+int cuasr_b200_srgemm_splitk_static(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  const int st = validate(desc, args);
+  if (st != CUASR_STATUS_SUCCESS) return st;
+  if (splitk_workspace_bytes(*desc, *args) > CUASR_B200_STATIC_SCRATCH_BYTES)
+    return CUASR_STATUS_ERROR_STATIC_SCRATCH_TOO_SMALL;
+  void* scratch = nullptr;
+  if (static_scratch_address(&scratch) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+  cuasr_b200_args_t with_scratch = *args;
+  with_scratch.workspace = scratch;
+  with_scratch.workspace_bytes = CUASR_B200_STATIC_SCRATCH_BYTES;
+  return run(desc, &with_scratch, with_scratch.split_k_slices);
+}
+
 int cuasr_b200_device_status(void* stream) {
   DeviceState* dev = nullptr;
   if (!device_state(&dev)) return -1;
@@ -406,6 +443,8 @@ const char* cuasr_b200_status_string(int status) {
     case CUASR_STATUS_ERROR_NOT_SUPPORTED: return "not supported";
     case CUASR_STATUS_ERROR_WORKSPACE_NULL: return "workspace null";
     case CUASR_STATUS_ERROR_INTERNAL: return "internal error";
+    case CUASR_STATUS_ERROR_STATIC_SCRATCH_TOO_SMALL:
+      return "problem needs more scratch than the library's static scratch array holds";
     default: return "unknown status";
   }
 }

@@ -46,6 +46,7 @@ class Status(enum.IntEnum):
     kErrorNotSupported = 5
     kErrorWorkspaceNull = 6
     kErrorInternal = 7
+    kErrorStaticScratchTooSmall = 64  # this library only: see cuasr_b200_srgemm_splitk_static
 
 
 NUMPY_DTYPE = {DType.F32: np.float32, DType.F64: np.float64, DType.S32: np.int32, DType.U32: np.uint32}

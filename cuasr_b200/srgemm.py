@@ -157,6 +157,18 @@ class SrgemmSplitKParallel(_Operator):
     _splitk_parallel = True
 
 
+STATIC_SCRATCH_BYTES = 16 * 1024 * 1024 + 4096
+
+
+def srgemm_splitk_static(operator: _Operator, args: Arguments, stream=None) -> Status:
+    """Split-K SRGEMM on the library's built-in static scratch (cuasr_b200_srgemm_splitk_static): for callers
+    that are not allowed to allocate device memory.  `operator` supplies the ring, element type and layouts;
+    no workspace is passed.  Calls that overlap on the GPU share the scratch and must be serialised."""
+    packed = operator._pack(args, None, 0, stream)
+    lib = _lib.load()
+    return Status(lib.cuasr_b200_srgemm_splitk_static(ctypes.byref(operator._desc), ctypes.byref(packed)))
+
+
 def device_status(stream=None) -> int:
     """Synchronises `stream` and returns the device-side status word (0 = ok)."""
     return int(_lib.load().cuasr_b200_device_status(_stream_handle(stream)))

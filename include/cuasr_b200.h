@@ -91,6 +91,29 @@ CUASR_B200_API int cuasr_b200_srgemm_splitk_can_implement(const cuasr_b200_desc_
 CUASR_B200_API size_t cuasr_b200_srgemm_splitk_workspace_size(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 CUASR_B200_API int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 
+/* Split-K SRGEMM for callers that cannot allocate device memory.  (No counterpart in the reference, whose
+ * SrgemmSplitKParallel always takes a caller-allocated workspace.)
+ *
+ * Some hosts of this library may not call cudaMalloc at the point where they need a split-K product: code
+ * running inside a framework that owns all device memory and hands out none for scratch, plugins invoked
+ * under a "no allocation after start-up" rule (real-time or long-running services that must not fragment or
+ * fail on memory late), and callers that only hold the operand buffers they were given.  For them this entry
+ * point does what cuasr_b200_srgemm_splitk does, but the slice partials and tile counters live in a static
+ * device array that is part of the library image, so `workspace` / `workspace_bytes` in `args` are ignored
+ * and no cudaMalloc, cudaFree or other allocating call is made.  Inputs and outputs are still the caller's.
+ *
+ * Limits and rules:
+ *  - the array holds CUASR_B200_STATIC_SCRATCH_BYTES bytes; every GPU that loads the library carries it
+ *    until the process exits.  A problem that needs more (see cuasr_b200_srgemm_splitk_workspace_size)
+ *    is refused with CUASR_STATUS_ERROR_STATIC_SCRATCH_TOO_SMALL and nothing is launched;
+ *  - the first call on each device looks up the array's device address (a one-time, synchronous set-up, done
+ *    with that device current); make that first call before starting any stream capture;
+ *  - every call on a device shares the one array, which keeps whatever the previous call left in it: the
+ *    counters are cleared on the stream at the start of each call, the partials are fully overwritten
+ *    before they are read; two calls that overlap on the GPU (different streams) race on it -- serialise them. */
+#define CUASR_B200_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u + 4096u)
+CUASR_B200_API int cuasr_b200_srgemm_splitk_static(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
+
 /* Reads (and clears) the device-side status word of the current device after synchronising `stream`:
  * 0 = every kernel of this library ran to completion; otherwise a bounded wait inside a kernel expired
  * (1: tile never arrived, 2: stage never released, 3: peer flag never set).  This call blocks. */

@@ -51,7 +51,10 @@ typedef enum cuasr_status {
   CUASR_STATUS_ERROR_INVALID_PROBLEM     = 4,
   CUASR_STATUS_ERROR_NOT_SUPPORTED       = 5,
   CUASR_STATUS_ERROR_WORKSPACE_NULL      = 6,
-  CUASR_STATUS_ERROR_INTERNAL            = 7
+  CUASR_STATUS_ERROR_INTERNAL            = 7,
+  /* Not a cutlass::Status value: the problem needs more scratch than the library's built-in static
+   * scratch array holds (only returned by cuasr_b200_srgemm_splitk_static). */
+  CUASR_STATUS_ERROR_STATIC_SCRATCH_TOO_SMALL = 64
 } cuasr_status_t;
 
 #ifdef __cplusplus
