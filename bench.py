@@ -2,14 +2,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Default workload (`minplus_f32_8192`): min-plus fp32 SRGEMM D = min(C, A (x) B) with M = N = K = 8192, all
-matrices column-major, A and B uniform in [0, 100) from a seed, C filled with the additive identity.  One step
-is one SRGEMM; at N > 1 GPUs the columns of D (contiguous blocks of a column-major matrix) are sharded over
-the ranks and the step ends with an all-gather of D, which is exactly one squaring step of the sharded
-all-pairs-shortest-paths solve.  Prints ONE JSON line on rank 0.
+Default workload `minplus_f32_8192`: min-plus fp32 SRGEMM D = min(C, A (x) B), M = N = K = 8192, all matrices
+column-major, A and B uniform in [0, 100) from a seed, C filled with the additive identity.  One step is one
+SRGEMM.  At N > 1 GPUs the columns of D (contiguous blocks of a column-major matrix) are sharded over the ranks
+and the step ends with an all-gather of D: exactly one squaring step of the sharded all-pairs-shortest-paths
+solve.  Rank 0 prints ONE JSON line.  The other workloads of cuasr_b200/workloads.py run the same way on one GPU.
 
-`--impl reference` times the reference's own host SRGEMM (oracle/_ref, else the C restatement in oracle/)
-on the host cores, on a bounded sample of the same workload.
+`--impl reference` times the reference's own host SRGEMM (oracle/_ref when it was built, else the C restatement
+in oracle/) on the host cores, on a bounded sample of the same workload.
 """
 from __future__ import annotations
 
@@ -25,13 +25,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOADS = {
-    # name: (n, description)
-    "minplus_f32_8192": 8192,
-    "minplus_f32_4096": 4096,
-    "minplus_f32_16384": 16384,
-}
-SEED_A, SEED_B = 3090, 3091  # the seeds of examples/00_minplus_srgemm/minplus_srgemm.cu:108-110
+METRIC = "minplus_f32_srgemm_throughput"
 
 
 def measured_peaks():
@@ -82,53 +76,88 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-def host_operands(n: int, rows_of_d: int | None = None):
-    """Column-major A (n x n), B (n x n) as flat numpy float32 arrays (the CPU arm's inputs)."""
-    from cuasr_b200 import datagen
-    A = datagen.uniform_f32(SEED_A, n * n, 0.0, 100.0).numpy()
-    B = datagen.uniform_f32(SEED_B, n * n, 0.0, 100.0).numpy()
-    return A, B
+def identity_of(wl):
+    from cuasr_b200 import RINGS, identity
+    return identity(RINGS[wl.ring][0], wl.dtype) if wl.add_identity is None else wl.add_identity
 
 
-def cpu_arm(n: int, cols: int, repeats: int = 1, warmup: int = 0):
-    """Times the CPU SRGEMM on the first `cols` columns of D (D[:, :cols] = A (x) B[:, :cols]; 2 n^2 cols ops).
-    Returns (GOP/s, kind, cores, seconds per repeat)."""
+def cpu_sample(wl, lines: int):
+    """Host operands for the first `lines` storage lines of D (columns of a column-major D, rows of a row-major
+    one): returns (mnk, A, lda, B, ldb, C, ldc) as numpy arrays.  The sampled operand is the one whose lines
+    follow D's lines (B for column-major D, A for row-major D); the other operand is needed in full."""
+    import numpy as np
+    from cuasr_b200 import Layout
+    from cuasr_b200.semiring import NUMPY_DTYPE
+
+    np_t = NUMPY_DTYPE[wl.dtype]
+
+    def host(which, count=None):
+        t = wl.operand(which, "cpu", 0, count).numpy()
+        return t.view(np.uint32) if np_t == np.uint32 else t
+
+    ident = identity_of(wl)
+    if wl.layouts[2] == Layout.COLUMN_MAJOR:
+        assert wl.layouts[1] == Layout.COLUMN_MAJOR
+        A, B = host("A"), host("B", wl.k * lines)
+        mnk = (wl.m, lines, wl.k)
+        C = np.full(wl.m * lines, ident, np_t)
+        lda = wl.m if wl.layouts[0] == Layout.COLUMN_MAJOR else wl.k
+        return mnk, A, lda, B, wl.k, C, wl.m
+    assert wl.layouts[0] == Layout.ROW_MAJOR
+    A, B = host("A", wl.k * lines), host("B")
+    mnk = (lines, wl.n, wl.k)
+    C = np.full(lines * wl.n, ident, np_t)
+    ldb = wl.k if wl.layouts[1] == Layout.COLUMN_MAJOR else wl.n
+    return mnk, A, wl.k, B, ldb, C, wl.n
+
+
+def cpu_run(wl, lines: int, repeats: int = 1, warmup: int = 0):
+    """Times the CPU SRGEMM on a `lines`-wide sample.  Returns (GOP/s, kind, cores, seconds, D)."""
     import numpy as np
     import oracle
-    from cuasr_b200 import DType, Layout, Op, identity
+    from cuasr_b200 import RINGS
 
     use_ref = oracle.have_ref()
     fn = oracle.ref_srgemm if use_ref else oracle.srgemm
     cores = oracle.max_threads(use_ref)
-    A, B = host_operands(n)
-    ident = identity(Op.MINIMUM, DType.F32)
-    C = np.full(n * cols, ident, np.float32)
-    D = np.empty(n * cols, np.float32)
-    col = Layout.COLUMN_MAJOR
+    mnk, A, lda, B, ldb, C, ldc = cpu_sample(wl, lines)
+    D = np.empty_like(C)
+    add_op, mul_op = RINGS[wl.ring]
+    alpha = np.asarray(wl.alpha).astype(C.dtype)
+    beta = np.asarray(wl.beta).astype(C.dtype)
     times = []
     for i in range(warmup + repeats):
         t0 = time.perf_counter()
-        fn(Op.MINIMUM, Op.PLUS, DType.F32, (col, col, col), (n, cols, n), 0.0, A, n, B, n, 0.0, C, n, D, n, ident, cores)
+        fn(add_op, mul_op, wl.dtype, wl.layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D, ldc, identity_of(wl), cores)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
-    return 2.0 * n * n * cols / sec / 1e9, ("reference" if use_ref else "port"), cores, sec
+    return 2.0 * mnk[0] * mnk[1] * mnk[2] / sec / 1e9, ("reference" if use_ref else "port"), cores, sec, D
 
 
-def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+def sample_lines(wl, target_gop: float = 9.0) -> int:
+    """Lines of D whose product costs about `target_gop` GOP (a multiple of 32: the host SRGEMM works in
+    32 x 32 blocks, tools/include/cuasr/reference/srgemm/host_srgemm.h:56-57)."""
+    from cuasr_b200 import Layout
+    total = wl.n if wl.layouts[2] == Layout.COLUMN_MAJOR else wl.m
+    per_line = wl.ops / total
+    lines = int(target_gop * 1e9 / per_line) // 32 * 32
+    return max(32, min(total, lines))
+
+
+def run_reference(args, wl):
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    n = WORKLOADS[args.workload]
-    cols = 64 if n >= 8192 else 256
-    gops, kind, cores, sec = cpu_arm(n, cols, repeats=args.steps, warmup=args.warmup)
-    sample = f"D[:, :{cols}] of the {n}^3 problem per step ({2.0 * n * n * cols / 1e9:.1f} GOP), all {cores} host threads"
+    lines = sample_lines(wl)
+    gops, kind, cores, sec, _ = cpu_run(wl, lines, repeats=args.steps, warmup=args.warmup)
+    total_lines = wl.n if int(wl.layouts[2]) == 0 else wl.m
+    sample = (f"first {lines} storage lines of D of the {wl.m}x{wl.n}x{wl.k} problem per step "
+              f"({wl.ops / total_lines * lines / 1e9:.1f} GOP), all {cores} host threads")
     line = {
-        "impl": "reference", "metric": "minplus_f32_srgemm_throughput", "value": round(gops, 3), "unit": "GOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "m": n, "n": n, "k": n, "layout": "column-major A, B, C, D",
-                   "semiring": "min-plus"},
+        "impl": "reference", "metric": metric_name(wl), "value": round(gops, 3), "unit": "GOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": wl.dtype.name.lower(), "data": "synthetic",
+        "config": workload_config(wl),
         "cpu_baseline": {"value": round(gops, 3), "unit": "GOP/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": round(gops, 3), "unit": "GOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -136,11 +165,27 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def run_ours(args):
+def metric_name(wl):
+    from cuasr_b200 import DType
+    if wl.ring == "minimum_plus" and wl.dtype == DType.F32:
+        return METRIC
+    return f"{wl.ring}_{wl.dtype.name.lower()}_srgemm_throughput"
+
+
+def workload_config(wl):
+    return {"workload": wl.name, "m": wl.m, "n": wl.n, "k": wl.k, "semiring": wl.ring,
+            "layout": "/".join("col" if int(l) == 0 else "row" for l in wl.layouts) + " (A/B/C,D)",
+            "split_k_slices": wl.split_k_slices}
+
+
+def run_ours(args, wl):
+    import numpy as np
     import torch
     import torch.distributed as dist
 
-    from cuasr_b200 import Arguments, DType, Layout, Op, Srgemm, Status, datagen, device_status, identity, launch_count
+    from cuasr_b200 import (Arguments, DType, Layout, RINGS, Srgemm, SrgemmSplitKParallel, Status, device_status,
+                            launch_count)
+    from cuasr_b200.workloads import TORCH_DTYPE
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -152,31 +197,44 @@ def run_ours(args):
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
 
-    n = WORKLOADS[args.workload]
-    assert n % world == 0
-    cols = n // world                      # columns of D (and of B) this rank owns
+    col_major_c = wl.layouts[2] == Layout.COLUMN_MAJOR
+    if world > 1:
+        assert col_major_c and wl.layouts[1] == Layout.COLUMN_MAJOR and wl.n % world == 0, \
+            "only column-major workloads shard over ranks"
+    m, n, k = wl.m, wl.n, wl.k
+    es = 8 if wl.dtype == DType.F64 else 4
+    tdt = TORCH_DTYPE[wl.dtype]
+    ident = identity_of(wl)
+    add_op, mul_op = RINGS[wl.ring]
+
+    # this rank's share: `cols` columns of D and of B (everything when world == 1)
+    cols = n // world
     c0 = rank * cols
-    ident = identity(Op.MINIMUM, DType.F32)
-    col = Layout.COLUMN_MAJOR
+    lda = m if wl.layouts[0] == Layout.COLUMN_MAJOR else k
+    ldb = k if wl.layouts[1] == Layout.COLUMN_MAJOR else n
+    ldc = m if col_major_c else n
+    A = wl.operand("A", dev)
+    B = wl.operand("B", dev, c0 * k, cols * k) if world > 1 else wl.operand("B", dev)
+    fill = float(ident) if tdt.is_floating_point else int(ident)
+    C = torch.full((m * n,), fill, dtype=tdt, device=dev)
+    D = torch.zeros(m * n, dtype=tdt, device=dev)
+    off = c0 * m * es if world > 1 else 0
 
-    # operands resident in HBM: full A, this rank's column block of B, full C and D (column-major, ld = n)
-    A = datagen.uniform_f32(SEED_A, n * n, 0.0, 100.0, device=dev)
-    B = datagen.uniform_f32(SEED_B, n * cols, 0.0, 100.0, device=dev, start=c0 * n)
-    C = torch.full((n * n,), float(ident), dtype=torch.float32, device=dev)
-    D = torch.zeros(n * n, dtype=torch.float32, device=dev)
-    es = 4
-    op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, col, col, col)
-    margs = Arguments((n, cols, n), (A, n), (B, n), (C.data_ptr() + c0 * n * es, n), (D.data_ptr() + c0 * n * es, n),
-                      (0.0, 0.0))
+    cls = SrgemmSplitKParallel if wl.split_k_slices > 1 else Srgemm
+    op = cls(add_op, mul_op, wl.dtype, *wl.layouts, add_identity=ident)
+    margs = Arguments((m, cols if world > 1 else n, k), (A, lda), (B, ldb), (C.data_ptr() + off, ldc),
+                      (D.data_ptr() + off, ldc), (wl.alpha, wl.beta), wl.split_k_slices)
+    ws = None
+    need = op.get_workspace_size(margs)
+    if need:
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream()
-    assert op.initialize(margs, None, stream) == Status.kSuccess
+    st = op.initialize(margs, ws, stream)
+    assert st == Status.kSuccess, st
 
-    def step():
-        st = op.run(stream)
-        if st != Status.kSuccess:
-            raise RuntimeError(f"SRGEMM launch failed: {st!r}")
+    def gather():
         if world > 1:
-            dist.all_gather_into_tensor(D, D[c0 * n:(c0 + cols) * n])
+            dist.all_gather_into_tensor(D, D[c0 * m:(c0 + cols) * m])
 
     def barrier():
         if world > 1:
@@ -184,10 +242,12 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        step()
+        assert op.run(stream) == Status.kSuccess
+        gather()
     barrier()
+    kernel_name = op.last_kernel()
 
-    # ---- device-resident timing: CUDA events on the launching stream, kernel events inside ----
+    # ---- device-resident timing: CUDA events on the launching stream; kernel-only events inside ----
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     launches0 = launch_count()
@@ -198,29 +258,25 @@ def run_ours(args):
             kev[i][0].record(stream)
             st = op.run(stream)
             kev[i][1].record(stream)
-            if world > 1:
-                dist.all_gather_into_tensor(D, D[c0 * n:(c0 + cols) * n])
+            gather()
         ev1.record(stream)
         barrier()
     launches = launch_count() - launches0
     assert st == Status.kSuccess and device_status() == 0
-    ms_total = ev0.elapsed_time(ev1)
-    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in kev)
-    t = torch.tensor([ms_total, kernel_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([ev0.elapsed_time(ev1), statistics.mean(a.elapsed_time(b) for a, b in kev)],
+                     dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, kernel_ms = float(t[0]), float(t[1])
-    ms_per_step = ms_total / args.steps
-    ops_per_step = 2.0 * n * n * n
-    value = ops_per_step / (ms_per_step * 1e-3) / 1e9
+    ms_per_step, kernel_ms = float(t[0]) / args.steps, float(t[1])
+    value = wl.ops / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the host-buffer call: pinned host operands in, D out, every step ----
-    hA = torch.empty(n * n, dtype=torch.float32).pin_memory()
-    hB = torch.empty(n * cols, dtype=torch.float32).pin_memory()
-    hC = torch.empty(n * cols, dtype=torch.float32).pin_memory()
-    hD = torch.empty(n * cols, dtype=torch.float32).pin_memory()
-    hA.copy_(A); hB.copy_(B); hC.fill_(float(ident))
-    Cs, Ds = C[c0 * n:(c0 + cols) * n], D[c0 * n:(c0 + cols) * n]
+    hA = torch.empty(A.numel(), dtype=tdt).pin_memory(); hA.copy_(A)
+    hB = torch.empty(B.numel(), dtype=tdt).pin_memory(); hB.copy_(B)
+    share = m * cols
+    Cs, Ds = C[c0 * m: c0 * m + share], D[c0 * m: c0 * m + share]
+    hC = torch.empty(share, dtype=tdt).pin_memory(); hC.fill_(fill)
+    hD = torch.empty(share, dtype=tdt).pin_memory()
     e2e_steps = max(1, min(args.steps, 5))
 
     def e2e_step():
@@ -241,52 +297,45 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t[0]) / e2e_steps
-    e2e_value = ops_per_step / (e2e_ms * 1e-3) / 1e9
     h2d = (hA.numel() + hB.numel() + hC.numel()) * es
     d2h = hD.numel() * es
 
-    # ---- spot check of the timed result against the CPU oracle (a few columns of D) ----
-    parity = None
-    cpu = None
+    # ---- rank 0: spot check against the CPU oracle, CPU baseline, JSON line ----
     if rank == 0:
-        import numpy as np
-        import oracle
-        check_cols = 4
-        hostA, hostB = host_operands(n)
-        want = np.empty(n * check_cols, np.float32)
-        Cc = np.full(n * check_cols, ident, np.float32)
-        fn = oracle.ref_srgemm if oracle.have_ref() else oracle.srgemm
-        fn(Op.MINIMUM, Op.PLUS, DType.F32, (col, col, col), (n, check_cols, n), 0.0, hostA, n, hostB, n, 0.0, Cc, n,
-           want, n, ident, 0)
-        got = D[: n * check_cols].cpu().numpy()
-        parity = bool(np.array_equal(got, want))
+        _, _, _, _, want = cpu_run(wl, 32)
+        got = D[: want.size].cpu().numpy()
+        got = got.view(np.uint32) if want.dtype == np.uint32 else got
+        if wl.ring == "plus_multiplies":
+            parity = bool(np.allclose(got, want, rtol=0, atol=8 * k * np.finfo(want.dtype).eps * (wl.hi ** 2)))
+        else:
+            parity = bool(np.array_equal(got, want))
+        cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            sample_cols = 64 if n >= 8192 else 256
-            gops, kind, cores, sec = cpu_arm(n, sample_cols, repeats=1, warmup=0)
+            lines = sample_lines(wl)
+            gops, kind, cores, sec, _ = cpu_run(wl, lines)
             cpu = {"value": round(gops, 3), "unit": "GOP/s", "cores": cores, "kind": kind,
-                   "sample": f"D[:, :{sample_cols}] of the {n}^3 problem, one pass ({sec:.1f} s), all {cores} host threads"}
-
-    if rank == 0:
+                   "sample": f"first {lines} storage lines of D, one pass ({sec:.1f} s), all {cores} host threads"}
         peaks, peak_kind = measured_peaks()
-        props = torch.cuda.get_device_properties(dev)
-        sms = props.multi_processor_count
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
         peak_tops = sms * 128 * 2 * peaks["sm_max_mhz"] * 1e6 / 1e12
-        k_ops = 2.0 * n * cols * n                     # one launch on one rank
-        achieved = k_ops / (kernel_ms * 1e-3) / 1e12
-        algorithmic_bytes = es * (n * n + n * cols + 2 * n * cols)   # A + B block + C block read + D block written
+        achieved = (wl.ops / world) / (kernel_ms * 1e-3) / 1e12
+        algorithmic_bytes = es * (m * k + k * cols + 2 * m * cols)   # A + B block + C block read + D block written
         line = {
-            "metric": "minplus_f32_srgemm_throughput", "value": round(value, 2), "unit": "GOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "m": n, "n": n, "k": n, "layout": "column-major A, B, C, D",
-                       "semiring": "min-plus", "sharding": f"{cols} columns of D per rank" + (", all-gather of D" if world > 1 else ""),
-                       "l2": "operands (3 x %d MiB) exceed the 126 MB L2" % (n * n * es >> 20)},
-            "e2e": {"value": round(e2e_value, 2), "unit": "GOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
+            "metric": metric_name(wl),
+            "value": round(value, 2), "unit": "GOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": wl.dtype.name.lower(), "data": "synthetic",
+            "config": dict(workload_config(wl), kernel=kernel_name,
+                           sharding=f"{cols} columns of D per rank" + (", all-gather of D" if world > 1 else ""),
+                           l2="operands exceed the 126 MB L2" if es * (m * k + k * n) > 126e6 else
+                              "L2 flushed between steps by the other operands' traffic: NO (operands fit L2)"),
+            "e2e": {"value": round(wl.ops / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
-            "roofline": {"bound": "fp32 CUDA cores (issue/ALU pipes); HBM is three orders below", "achieved": round(achieved, 3),
-                         "peak": round(peak_tops, 2), "unit": "TOP/s", "frac": round(achieved / peak_tops, 4),
+            "roofline": {"bound": "CUDA cores (issue / register-file ports); HBM is orders of magnitude below",
+                         "achieved": round(achieved, 3), "peak": round(peak_tops, 2), "unit": "TOP/s",
+                         "frac": round(achieved / peak_tops, 4),
                          "peak_source": f"{sms} SMs x 128 lanes x 2 x sm_max_mhz ({peak_kind} clock {peaks['sm_max_mhz']:.0f} MHz)",
                          "kernel_ms": round(kernel_ms, 4),
                          "hbm_achieved_gbs": round(algorithmic_bytes / (kernel_ms * 1e-3) / 1e9, 2),
@@ -300,6 +349,8 @@ def run_ours(args):
 
 
 def main():
+    from cuasr_b200.workloads import WORKLOADS
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -308,11 +359,12 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="minplus_f32_8192")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    wl = WORKLOADS[args.workload]
     if args.impl == "reference":
-        run_reference(args)
+        run_reference(args, wl)
     else:
-        run_ours(args)
+        args.warmup = max(args.warmup, 3)
+        run_ours(args, wl)
 
 
 if __name__ == "__main__":

@@ -29,7 +29,7 @@ constexpr bool tma_instantiated() {
                         (MUL == CUASR_OP_BIT_AND || MUL == CUASR_OP_BINARY_AND) &&
                         !(ADD == CUASR_OP_BIT_OR && MUL == CUASR_OP_BINARY_AND);
   if (std::is_same<T, float>::value) return tropical || minmax || times;
-  if (std::is_same<T, double>::value) return false;
+  if (std::is_same<T, double>::value) return tropical || minmax || times;
   return bits;  // int32_t, uint32_t
 }
 

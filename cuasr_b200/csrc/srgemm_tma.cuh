@@ -239,24 +239,40 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               acc[i][j] = RingT::mac2(acc[i][j], a[i][e], b[j][e], a[i][e + 1], b[j][e + 1]);
       };
 
-      T a0[8][EV], b0[8][EV], a1[8][EV], b1[8][EV];
-      load_a(a0, 0);
-      load_b(b0, 0);
+      if constexpr (sizeof(T) == 4) {
+        // 4-byte elements: operand fragments are double-buffered in registers (64 + 4 x 32 registers)
+        T a0[8][EV], b0[8][EV], a1[8][EV], b1[8][EV];
+        load_a(a0, 0);
+        load_b(b0, 0);
 #pragma unroll 1
-      for (int chunk = 0; chunk < kChunks; chunk += 2) {
-        load_a(a1, chunk + 1);
-        load_b(b1, chunk + 1);
-        compute(a0, b0);
-        if (chunk + 2 < kChunks) {
-          load_a(a0, chunk + 2);
-          load_b(b0, chunk + 2);
-        } else {
-          // every load from this stage has been issued and, being volatile asm in program order with
-          // the uses below, has its data in registers before the math that follows retires; release it
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&empty_bar[s]);
+        for (int chunk = 0; chunk < kChunks; chunk += 2) {
+          load_a(a1, chunk + 1);
+          load_b(b1, chunk + 1);
+          compute(a0, b0);
+          if (chunk + 2 < kChunks) {
+            load_a(a0, chunk + 2);
+            load_b(b0, chunk + 2);
+          } else {
+            // every load from this stage has been issued; the arrive below is a release, so those loads
+            // have read shared memory before the producer can see the stage as free
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);
+          }
+          compute(a1, b1);
         }
-        compute(a1, b1);
+      } else {
+        // 8-byte elements: the 8 x 8 accumulators alone take 128 registers, so one fragment set is live
+        T a0[8][EV], b0[8][EV];
+#pragma unroll 1
+        for (int chunk = 0; chunk < kChunks; ++chunk) {
+          load_a(a0, chunk);
+          load_b(b0, chunk);
+          if (chunk + 1 == kChunks) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);
+          }
+          compute(a0, b0);
+        }
       }
     }
 
