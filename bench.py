@@ -217,8 +217,19 @@ def run_ours(args, wl):
     B = wl.operand("B", dev, c0 * k, cols * k) if world > 1 else wl.operand("B", dev)
     fill = float(ident) if tdt.is_floating_point else int(ident)
     C = torch.full((m * n,), fill, dtype=tdt, device=dev)
-    D = torch.zeros(m * n, dtype=tdt, device=dev)
+    push = world > 1 and args.exchange == "push"
+    peer_d = []
+    if push:
+        import torch.distributed._symmetric_memory as symm_mem
+        D = symm_mem.empty(m * n, dtype=tdt, device=dev)
+        handle = symm_mem.rendezvous(D, dist.group.WORLD)
+        peer_d = [int(p) for p in handle.buffer_ptrs]
+        D.zero_()
+    else:
+        D = torch.zeros(m * n, dtype=tdt, device=dev)
     off = c0 * m * es if world > 1 else 0
+    extras = [p + off for r, p in enumerate(peer_d) if r != rank]
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
 
     cls = SrgemmSplitKParallel if wl.split_k_slices > 1 else Srgemm
     op = cls(add_op, mul_op, wl.dtype, *wl.layouts, add_identity=ident)
@@ -232,8 +243,13 @@ def run_ours(args, wl):
     st = op.initialize(margs, ws, stream)
     assert st == Status.kSuccess, st
 
+    def launch():
+        return op.run_push(extras, stream) if push else op.run(stream)
+
     def gather():
-        if world > 1:
+        if push:
+            dist.all_reduce(flag)          # stream-ordered: every rank's stores into every D are complete
+        elif world > 1:
             dist.all_gather_into_tensor(D, D[c0 * m:(c0 + cols) * m])
 
     def barrier():
@@ -242,7 +258,7 @@ def run_ours(args, wl):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        assert op.run(stream) == Status.kSuccess
+        assert launch() == Status.kSuccess
         gather()
     barrier()
     kernel_name = op.last_kernel()
@@ -256,7 +272,7 @@ def run_ours(args, wl):
         ev0.record(stream)
         for i in range(args.steps):
             kev[i][0].record(stream)
-            st = op.run(stream)
+            st = launch()
             kev[i][1].record(stream)
             gather()
         ev1.record(stream)
@@ -281,8 +297,9 @@ def run_ours(args, wl):
 
     def e2e_step():
         A.copy_(hA, non_blocking=True); B.copy_(hB, non_blocking=True); Cs.copy_(hC, non_blocking=True)
-        if op.run(stream) != Status.kSuccess:
+        if launch() != Status.kSuccess:
             raise RuntimeError("SRGEMM launch failed")
+        gather()
         hD.copy_(Ds, non_blocking=True)
 
     e2e_step()
@@ -326,7 +343,9 @@ def run_ours(args, wl):
             "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": wl.dtype.name.lower(), "data": "synthetic",
             "config": dict(workload_config(wl), kernel=kernel_name,
-                           sharding=f"{cols} columns of D per rank" + (", all-gather of D" if world > 1 else ""),
+                           sharding=f"{cols} columns of D per rank" + (
+                               "" if world == 1 else ", epilogue stores D to every peer + barrier" if push
+                               else ", NCCL all-gather of D"),
                            l2="operands exceed the 126 MB L2" if es * (m * k + k * n) > 126e6 else
                               "L2 flushed between steps by the other operands' traffic: NO (operands fit L2)"),
             "e2e": {"value": round(wl.ops / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GOP/s", "h2d_bytes_per_step": h2d,
@@ -358,6 +377,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="minplus_f32_8192")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--exchange", choices=("push", "allgather"), default="push",
+                    help="N > 1: how D reaches every rank -- stored to peers by the SRGEMM epilogue, or NCCL all-gather")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -1,0 +1,145 @@
+"""All-pairs shortest paths by repeated min-plus squaring, sharded over the GPUs of one node.
+
+The reference stops at one GPU; its README only motivates the epilogue (+) with C by distributed APSP
+(README.md:338-342).  This layer is the multi-GPU side the north star adds:
+
+    D  <-  min(D, D (x) D)        ceil(log2 n) times, D the n x n matrix of path lengths (column-major)
+
+Rank g of G owns n/G consecutive columns (one contiguous block of a column-major matrix).  A squaring step is one
+SRGEMM per rank, `D_next[:, block] = min(D_cur[:, block], D_cur (x) D_cur[:, block])`, followed by the only
+exchange of the algorithm: every rank needs the whole of D_next.  Two exchange modes:
+
+  "allgather"  NCCL all-gather of D_next (torch.distributed) after the kernel.
+  "push"       the SRGEMM epilogue itself stores each finished tile into every rank's D_next through peer
+               pointers (cuasr_b200_srgemm_push), so the transfer overlaps the computation tile by tile; the
+               step ends with a stream-ordered barrier.  Peer pointers come from torch symmetric memory.
+
+The host logic (sharding, buffer rotation, exchange) is independent of the device: `ShardedSquaring` drives a
+small backend interface, `CudaBackend` is the product, and the CPU tests plug in a gloo/numpy backend.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence
+
+from .semiring import DType, Layout, Op, identity
+
+
+class ShardedSquaring:
+    """Sharding and buffer rotation of the repeated-squaring solve; all data movement goes through `backend`."""
+
+    def __init__(self, n: int, rank: int, world: int, backend):
+        if n % world != 0:
+            raise ValueError(f"n = {n} is not divisible by the {world} ranks")
+        self.n, self.rank, self.world, self.backend = n, rank, world, backend
+        self.cols = n // world
+        self.c0 = rank * self.cols
+        self.cur, self.nxt = 0, 1         # indices of the two full-size matrices the backend holds
+        self.steps_done = 0
+
+    @staticmethod
+    def squarings_needed(n: int) -> int:
+        """Paths have at most n - 1 edges and every squaring doubles the covered length: ceil(log2 n) steps."""
+        return max(1, math.ceil(math.log2(n)))
+
+    def step(self) -> None:
+        b = self.backend
+        b.srgemm_block(self.cur, self.nxt, self.c0, self.cols)   # D_next[:, block] (and, in push mode, every peer's)
+        b.exchange(self.nxt, self.c0, self.cols)                 # afterwards every rank holds all of D_next
+        self.cur, self.nxt = self.nxt, self.cur
+        self.steps_done += 1
+
+    def solve(self, squarings: Optional[int] = None) -> int:
+        squarings = self.squarings_needed(self.n) if squarings is None else squarings
+        for _ in range(squarings):
+            self.step()
+        return squarings
+
+    def result(self):
+        return self.backend.matrix(self.cur)
+
+
+class CudaBackend:
+    """Two n x n fp32 matrices per GPU, the min-plus SRGEMM of this library, and the exchange over NVLink."""
+
+    def __init__(self, n: int, rank: int, world: int, device, mode: str = "push", group=None,
+                 true_infinity: bool = True):
+        import torch
+        import torch.distributed as dist
+
+        from .srgemm import Arguments, Srgemm, Status
+
+        if mode not in ("push", "allgather"):
+            raise ValueError(mode)
+        self.n, self.rank, self.world, self.device, self.mode = n, rank, world, device, mode
+        self.torch, self.dist, self.group = torch, dist, group
+        self.Status, self.Arguments = Status, Arguments
+        self.inf = math.inf if true_infinity else float(identity(Op.MINIMUM, DType.F32))
+        self.peer_ptrs: List[List[int]] = [[], []]
+        if world > 1 and mode == "push":
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.bufs = [symm_mem.empty(n * n, dtype=torch.float32, device=device) for _ in range(2)]
+            self._handles = [symm_mem.rendezvous(t, dist.group.WORLD if group is None else group) for t in self.bufs]
+            self.peer_ptrs = [[int(p) for p in h.buffer_ptrs] for h in self._handles]
+        else:
+            self.bufs = [torch.empty(n * n, dtype=torch.float32, device=device) for _ in range(2)]
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        col = Layout.COLUMN_MAJOR
+        self.op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, col, col, col, add_identity=self.inf)
+        self.launches = 0
+
+    # -- data ---------------------------------------------------------------------------------------------
+    def load(self, which: int, flat) -> None:
+        self.bufs[which].copy_(flat)
+
+    def matrix(self, which: int):
+        return self.bufs[which]
+
+    # -- the two operations ShardedSquaring needs -----------------------------------------------------------
+    def srgemm_block(self, cur: int, nxt: int, c0: int, cols: int) -> None:
+        n, es = self.n, 4
+        src, dst = self.bufs[cur], self.bufs[nxt]
+        off = c0 * n * es
+        # A = D_cur (n x n), B = C = D_cur[:, block], D = D_next[:, block]; alpha = beta = 0 = the (x) identity
+        args = self.Arguments((n, cols, n), (src, n), (src.data_ptr() + off, n), (src.data_ptr() + off, n),
+                              (dst.data_ptr() + off, n), (0.0, 0.0))
+        stream = self.torch.cuda.current_stream(self.device)
+        st = self.op.initialize(args, None, stream)
+        if st != self.Status.kSuccess:
+            raise RuntimeError(f"SRGEMM rejected the squaring step: {st!r}")
+        if self.world > 1 and self.mode == "push":
+            extras = [p + off for r, p in enumerate(self.peer_ptrs[nxt]) if r != self.rank]
+            st = self.op.run_push(extras, stream)
+        else:
+            st = self.op.run(stream)
+        if st != self.Status.kSuccess:
+            raise RuntimeError(f"SRGEMM launch failed: {st!r}")
+        self.launches += 1
+
+    def exchange(self, nxt: int, c0: int, cols: int) -> None:
+        if self.world == 1:
+            return
+        if self.mode == "allgather":
+            buf = self.bufs[nxt]
+            self.dist.all_gather_into_tensor(buf, buf[c0 * self.n:(c0 + cols) * self.n], group=self.group)
+        else:
+            # every rank's kernel has written into every rank's D_next; a stream-ordered collective on one word
+            # orders "all kernels of this step are done" before anything that follows on any rank
+            self.dist.all_reduce(self._flag, group=self.group)
+
+
+def random_graph(n: int, p: float, seed: int, device, absent: float = math.inf, rows: Optional[Sequence[int]] = None):
+    """Flat column-major (= row-major, the generator is symmetric) weighted adjacency matrix of a random directed
+    graph: each edge present with probability p, integer weights uniform in [1, 100] stored as fp32, diagonal 0,
+    absent edges = `absent`."""
+    import torch
+
+    from . import datagen
+
+    if rows is None:
+        return datagen.sparse_graph(seed, n, p, absent, dtype=torch.float32, device=device, weight_lo=1,
+                                    weight_hi=100, integer_weights=True)
+    start, count = rows
+    return datagen.sparse_graph(seed, n, p, absent, dtype=torch.float32, device=device, weight_lo=1, weight_hi=100,
+                                integer_weights=True, row_start=start, rows=count)

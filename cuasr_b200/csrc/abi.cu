@@ -213,8 +213,14 @@ size_t splitk_workspace_bytes(const cuasr_b200_desc_t& desc, const cuasr_b200_ar
   X(CUASR_OP_BIT_OR, CUASR_OP_BIT_AND)         \
   X(CUASR_OP_BIT_XOR, CUASR_OP_BINARY_AND)
 
+// Further destinations of the output (cuasr_b200_srgemm_push); empty for the ordinary entry points.
+struct ExtraOutputs {
+  int count = 0;
+  void* ptr[kMaxDestinations - 1] = {};
+};
+
 template <typename T>
-int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int slices) {
+int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int slices, const ExtraOutputs& extra) {
   DeviceState* dev = nullptr;
   if (!device_state(&dev)) return CUASR_STATUS_ERROR_INTERNAL;
   cudaStream_t stream = static_cast<cudaStream_t>(args.stream);
@@ -268,6 +274,13 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
       tp.C = static_cast<const T*>(p.c); tp.ldc = p.ldc;
       tp.D = static_cast<T*>(p.d); tp.ldd = p.ldd;
       tp.alpha = alpha; tp.beta = beta; tp.add_identity = add_id; tp.read_c = read_c;
+      tp.n_extra = extra.count;
+      bool vec = tma_ok(p.d, p.ldd) && (!read_c || tma_ok(p.c, p.ldc)) && p.n % (16 / (int)sizeof(T)) == 0;
+      for (int x = 0; x < extra.count; ++x) {
+        tp.extra_d[x] = static_cast<T*>(extra.ptr[x]);
+        vec = vec && reinterpret_cast<uintptr_t>(extra.ptr[x]) % 16 == 0;
+      }
+      tp.vector_epilogue = vec;
       tp.tiles_m = (p.m + kTileM - 1) / kTileM; tp.tiles_n = (p.n + kTileN - 1) / kTileN;
       tp.status = dev->status;
       tp.slices = slices;
@@ -296,6 +309,8 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
     gp.B = static_cast<const T*>(p.b); gp.b_row = p.b_kcontig ? 1 : p.ldb; gp.b_col = p.b_kcontig ? p.ldb : 1;
     gp.C = static_cast<const T*>(p.c); gp.ldc = p.ldc;
     gp.D = static_cast<T*>(p.d); gp.ldd = p.ldd;
+    gp.n_extra = extra.count;
+    for (int x = 0; x < extra.count; ++x) gp.extra_d[x] = static_cast<T*>(extra.ptr[x]);
     gp.alpha = alpha; gp.beta = beta; gp.add_identity = add_id; gp.read_c = read_c;
     gp.k_per_slice = (p.k + slices - 1) / slices;
     gp.partial = slices > 1 ? partial : nullptr;
@@ -327,12 +342,13 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
   return CUASR_STATUS_SUCCESS;
 }
 
-int run(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args, int slices) {
+int run(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args, int slices,
+        const ExtraOutputs& extra = ExtraOutputs()) {
   switch (desc->dtype) {
-    case CUASR_F32: return run_typed<float>(*desc, *args, slices);
-    case CUASR_F64: return run_typed<double>(*desc, *args, slices);
-    case CUASR_S32: return run_typed<int32_t>(*desc, *args, slices);
-    case CUASR_U32: return run_typed<uint32_t>(*desc, *args, slices);
+    case CUASR_F32: return run_typed<float>(*desc, *args, slices, extra);
+    case CUASR_F64: return run_typed<double>(*desc, *args, slices, extra);
+    case CUASR_S32: return run_typed<int32_t>(*desc, *args, slices, extra);
+    case CUASR_U32: return run_typed<uint32_t>(*desc, *args, slices, extra);
     default: return CUASR_STATUS_ERROR_INVALID_DATA_TYPE;
   }
 }
@@ -386,6 +402,23 @@ int cuasr_b200_srgemm(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* ar
   const int st = cuasr_b200_srgemm_can_implement(desc, args);
   if (st != CUASR_STATUS_SUCCESS) return st;
   return run(desc, args, args->split_k_slices);
+}
+
+int cuasr_b200_srgemm_push(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args, int n_extra,
+                           void* const* extra_d) {
+  const int st = cuasr_b200_srgemm_can_implement(desc, args);
+  if (st != CUASR_STATUS_SUCCESS) return st;
+  if (n_extra < 0 || n_extra > kMaxDestinations - 1 || (n_extra > 0 && extra_d == nullptr))
+    return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  ExtraOutputs extra;
+  extra.count = n_extra;
+  const size_t es = desc->dtype == CUASR_F64 ? 8 : 4;
+  for (int x = 0; x < n_extra; ++x) {
+    if (extra_d[x] == nullptr) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+    if (reinterpret_cast<uintptr_t>(extra_d[x]) % es != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+    extra.ptr[x] = extra_d[x];
+  }
+  return run(desc, args, args->split_k_slices, extra);
 }
 
 int cuasr_b200_srgemm_splitk_can_implement(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {

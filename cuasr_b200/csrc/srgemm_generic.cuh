@@ -18,6 +18,8 @@ struct GenericParams {
   const T* B;  long long b_row, b_col;   // element (k, n) of B at B[k * b_row + n * b_col]
   const T* C;  long long ldc;            // row-major, may alias D, may be null when !read_c
   T* D;        long long ldd;            // row-major
+  int n_extra;               // further copies of the output (same ld), possibly in peer-GPU memory
+  T* extra_d[7];
   T alpha, beta, add_identity;
   int read_c;                // epilogue uses C: D = add(mul(alpha, acc), mul(beta, C)); else D = mul(alpha, acc)
   // split-K: slice z of gridDim.z covers k in [z * k_per_slice, min(K, (z + 1) * k_per_slice)) and writes
@@ -95,6 +97,7 @@ srgemm_generic_kernel(GenericParams<typename RingT::Element> p) {
         T v = RingT::mul(p.alpha, acc[i][j]);
         if (p.read_c) v = RingT::add(v, RingT::mul(p.beta, p.C[(long long)m * p.ldc + n]));
         p.D[(long long)m * p.ldd + n] = v;
+        for (int x = 0; x < p.n_extra; ++x) p.extra_d[x][(long long)m * p.ldd + n] = v;
       }
     }
   }
@@ -114,6 +117,7 @@ splitk_reduce_kernel(GenericParams<typename RingT::Element> p, int slices) {
   T v = RingT::mul(p.alpha, r);
   if (p.read_c) v = RingT::add(v, RingT::mul(p.beta, p.C[(long long)m * p.ldc + n]));
   p.D[(long long)m * p.ldd + n] = v;
+  for (int x = 0; x < p.n_extra; ++x) p.extra_d[x][(long long)m * p.ldd + n] = v;
 }
 
 }  // namespace cuasr_b200

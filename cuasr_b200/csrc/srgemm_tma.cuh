@@ -42,15 +42,25 @@ constexpr int kConsumerRegs = 232;
 constexpr int kProducerRegs = 40;
 constexpr int kOperandStageBytes = kTileM * kTileKBytes;   // 16 KiB
 constexpr int kStageBytes = 2 * kOperandStageBytes;
-constexpr int kTmaSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kEpilogueWarpBytes = 8192;          // per consumer warp: staging for coalesced output rows
+constexpr int kEpilogueBytes = kConsumerWarps * kEpilogueWarpBytes;
+constexpr int kMaxDestinations = 8;               // output copies one launch can write (this GPU + peers)
+constexpr int kTmaSmemBytes =
+    kStages * kStageBytes + kEpilogueBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 
 template <typename T>
 struct TmaParams {
   int M, N, K;
   const T* C;  long long ldc;   // row-major; may alias D; may be null when !read_c
   T* D;        long long ldd;   // row-major
+  // Extra copies of the output: when n_extra > 0 every element of D is also stored to extra_d[i] (same
+  // leading dimension).  The pointers may be peer-GPU memory; this is how the sharded squaring step pushes
+  // its block of the result into every rank's next-iteration matrix while the tile is still in registers.
+  int n_extra;
+  T* extra_d[kMaxDestinations - 1];
   T alpha, beta, add_identity;
   int read_c;
+  int vector_epilogue;          // D, C and every extra_d are 16-byte aligned, ld * sizeof(T) % 16 == 0, N % EV == 0
   int tiles_m, tiles_n;
   unsigned int* status;         // device status word (see DeviceStatus)
   // split-K (slices > 1): slice z handles K tiles [z * k_tiles_per_slice, ...), the last slice takes the
@@ -100,7 +110,8 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint8_t* epi_smem = smem + kStages * kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_smem + kEpilogueBytes);
   uint64_t* empty_bar = full_bar + kStages;
   unsigned int* ticket_smem = reinterpret_cast<unsigned int*>(empty_bar + kStages);
 
@@ -314,8 +325,54 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               r = RingT::add(__ldcg(p.partial + ((long long)zz * p.M + m) * p.N + n), r);
             T v = RingT::mul(p.alpha, r);
             if (p.read_c) v = RingT::add(v, RingT::mul(p.beta, p.C[(long long)m * p.ldc + n]));
-            p.D[(long long)m * p.ldd + n] = v;
+            const long long off = (long long)m * p.ldd + n;
+            p.D[off] = v;
+            for (int x = 0; x < p.n_extra; ++x) p.extra_d[x][off] = v;
           }
+        }
+      }
+    } else if (p.vector_epilogue) {
+      // Coalesced path: the warp's 64 x 32 block goes through its private staging area (rows of 32
+      // elements, the 16-byte column groups XOR-swizzled by row & 7), then every lane handles 16 bytes of
+      // a row: C is read, the epilogue applied and the vector stored to D and to every extra copy.
+      constexpr int kRowsPerPass = kEpilogueWarpBytes / (32 * (int)sizeof(T));   // 64 (4-byte) or 32 (8-byte)
+      constexpr int kGroups = 32 / EV;                                            // 16-byte groups per row
+      T* stage = reinterpret_cast<T*>(epi_smem + warp * kEpilogueWarpBytes);
+#pragma unroll
+      for (int pass = 0; pass < 64 / kRowsPerPass; ++pass) {
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = row_of(i) - pass * kRowsPerPass;
+          if (r < 0 || r >= kRowsPerPass) continue;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int c = col_of(j);
+            const int group = ((c / EV) ^ (r & 7)) & (kGroups - 1);
+            stage[r * 32 + group * EV + (c % EV)] = acc[i][j];
+          }
+        }
+        __syncwarp();
+#pragma unroll 4
+        for (int idx = lane; idx < kRowsPerPass * kGroups; idx += 32) {
+          const int r = idx / kGroups, g = idx % kGroups;
+          const int m = m_base + pass * kRowsPerPass + r;
+          const int n = n_base + g * EV;
+          if (m >= p.M || n >= p.N) continue;
+          const int group = (g ^ (r & 7)) & (kGroups - 1);
+          alignas(16) T v[EV];
+          *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(stage + r * 32 + group * EV);
+#pragma unroll
+          for (int e = 0; e < EV; ++e) v[e] = RingT::mul(p.alpha, v[e]);
+          if (p.read_c) {
+            alignas(16) T c[EV];
+            *reinterpret_cast<uint4*>(c) = *reinterpret_cast<const uint4*>(p.C + (long long)m * p.ldc + n);
+#pragma unroll
+            for (int e = 0; e < EV; ++e) v[e] = RingT::add(v[e], RingT::mul(p.beta, c[e]));
+          }
+          const long long off = (long long)m * p.ldd + n;
+          *reinterpret_cast<uint4*>(p.D + off) = *reinterpret_cast<const uint4*>(v);
+          for (int x = 0; x < p.n_extra; ++x) *reinterpret_cast<uint4*>(p.extra_d[x] + off) = *reinterpret_cast<const uint4*>(v);
         }
       }
     } else {
@@ -329,7 +386,9 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           if (n >= p.N) continue;
           T v = RingT::mul(p.alpha, acc[i][j]);
           if (p.read_c) v = RingT::add(v, RingT::mul(p.beta, p.C[(long long)m * p.ldc + n]));
-          p.D[(long long)m * p.ldd + n] = v;
+          const long long off = (long long)m * p.ldd + n;
+          p.D[off] = v;
+          for (int x = 0; x < p.n_extra; ++x) p.extra_d[x][off] = v;
         }
       }
     }

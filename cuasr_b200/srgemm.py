@@ -135,6 +135,17 @@ class _Operator:
             self._args.stream = _stream_handle(stream)
         return Status(self._fn("")(ctypes.byref(self._desc), ctypes.byref(self._args)))
 
+    def run_push(self, extra_outputs, stream=None) -> Status:
+        """run(), with every element of D also stored to each matrix in `extra_outputs` (pointers or tensors
+        with D's layout and leading dimension; peer-GPU memory allowed): cuasr_b200_srgemm_push."""
+        if self._args is None or self._splitk_parallel:
+            return Status.kErrorInternal
+        if stream is not None:
+            self._args.stream = _stream_handle(stream)
+        ptrs = (ctypes.c_void_p * max(1, len(extra_outputs)))(*[_ptr(x) for x in extra_outputs])
+        return Status(self._lib.cuasr_b200_srgemm_push(ctypes.byref(self._desc), ctypes.byref(self._args),
+                                                       len(extra_outputs), ptrs))
+
     def __call__(self, args: Optional[Arguments] = None, workspace=None, stream=None,
                  workspace_bytes: int = 0) -> Status:
         if args is not None:

@@ -82,6 +82,15 @@ CUASR_B200_API size_t cuasr_b200_srgemm_workspace_size(const cuasr_b200_desc_t *
  * enqueues D = add(mul(alpha, A (x)(+) B), mul(beta, C)) and returns without waiting. */
 CUASR_B200_API int cuasr_b200_srgemm(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 
+/* cuasr_b200_srgemm whose epilogue also stores every element of D to `n_extra` (at most 7) further
+ * matrices with the same layout and leading dimension as D.  The extra pointers may be peer-GPU memory that
+ * this device can address (peer access enabled): this is the fused "compute + all-gather" step of the sharded
+ * repeated-squaring solve, where each rank pushes its block of D into every rank's next-iteration matrix while
+ * the tile is still on chip.  New in this library: the reference has no multi-GPU code (README.md:338-342 only
+ * motivates it).  Ordering across GPUs is the caller's job (a stream-ordered barrier after the launch). */
+CUASR_B200_API int cuasr_b200_srgemm_push(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args, int n_extra,
+                                          void *const *extra_d);
+
 /* SrgemmSplitKParallel::can_implement / get_workspace_size / operator()
  * (device/srgemm_splitk_parallel.h:220-235, :238-279, :333-348).  The reference needs
  * sizeof(element) * M * N * slices bytes of workspace and two launches; this library needs a little more

@@ -1,0 +1,105 @@
+"""Repeated-squaring APSP on the GPU against the CPU oracle and Floyd-Warshall; multi-GPU modes where two or more
+GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import oracle
+from cuasr_b200 import DType, Layout, Op
+from cuasr_b200.apsp import CudaBackend, ShardedSquaring, random_graph
+
+pytestmark = pytest.mark.gpu
+COL = Layout.COLUMN_MAJOR
+
+
+def cpu_apsp(flat, n, squarings):
+    cur = flat.copy()
+    inf = np.float32(np.inf)
+    for _ in range(squarings):
+        nxt = np.empty_like(cur)
+        oracle.srgemm(Op.MINIMUM, Op.PLUS, DType.F32, (COL, COL, COL), (n, n, n), 0.0, cur, n, cur, n, 0.0, cur, n,
+                      nxt, n, inf, 0)
+        cur = nxt
+    return cur
+
+
+def test_single_gpu_apsp_matches_cpu(cuda_device):
+    """Full solve at n = 1024 (the whole algorithm on the CPU as well), every squaring compared bit for bit."""
+    import torch
+    n, seed = 1024, 11
+    flat = random_graph(n, 0.01, seed, cuda_device)
+    backend = CudaBackend(n, 0, 1, cuda_device)
+    backend.load(0, flat)
+    solver = ShardedSquaring(n, 0, 1, backend)
+    host = flat.cpu().numpy()
+    for step in range(ShardedSquaring.squarings_needed(n)):
+        solver.step()
+        host = cpu_apsp(host, n, 1)
+        torch.cuda.synchronize()
+        assert np.array_equal(solver.result().cpu().numpy(), host), f"squaring {step} differs"
+    # the fixed point: one more squaring changes nothing, and distances satisfy the triangle inequality
+    again = cpu_apsp(host, n, 1)
+    assert np.array_equal(again, host)
+
+
+def test_apsp_blocks_at_full_size_property(cuda_device):
+    """n = 4096: sampled column blocks of one squaring against the oracle fed the same input."""
+    import torch
+    n = 4096
+    flat = random_graph(n, 0.01, 3, cuda_device)
+    backend = CudaBackend(n, 0, 1, cuda_device)
+    backend.load(0, flat)
+    solver = ShardedSquaring(n, 0, 1, backend)
+    solver.step()
+    solver.step()
+    before = backend.matrix(solver.cur).clone()
+    solver.step()
+    torch.cuda.synchronize()
+    src = before.cpu().numpy()
+    got = solver.result().cpu().numpy()
+    inf = np.float32(np.inf)
+    for c0 in (0, 1504, 4064):
+        blk = slice(c0 * n, (c0 + 32) * n)
+        want = np.empty(32 * n, np.float32)
+        oracle.srgemm(Op.MINIMUM, Op.PLUS, DType.F32, (COL, COL, COL), (n, 32, n), 0.0, src, n,
+                      np.ascontiguousarray(src[blk]), n, 0.0, np.ascontiguousarray(src[blk]), n, want, n, inf, 0)
+        assert np.array_equal(got[blk], want), f"columns {c0}..{c0 + 31}"
+    # squaring never lengthens a path
+    assert bool((solver.result() <= before).all())
+
+
+def _rank(rank, world, port, n, seed, mode, out):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    backend = CudaBackend(n, rank, world, dev, mode=mode)
+    backend.load(0, random_graph(n, 0.01, seed, dev))
+    solver = ShardedSquaring(n, rank, world, backend)
+    solver.solve()
+    torch.cuda.synchronize()
+    out[(mode, rank)] = solver.result().cpu().numpy()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["allgather", "push"])
+def test_multi_gpu_apsp(mode):
+    import torch
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    n, seed = 1024, 21
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = mp.Manager().dict()
+    mp.spawn(_rank, args=(world, port, n, seed, mode, out), nprocs=world, join=True)
+    want = cpu_apsp(random_graph(n, 0.01, seed, "cpu").numpy(), n, ShardedSquaring.squarings_needed(n))
+    for rank in range(world):
+        assert np.array_equal(out[(mode, rank)], want), f"{mode}: rank {rank} differs from the CPU solve"
