@@ -1,5 +1,5 @@
-// Thin wrappers over the sm_100a PTX this library uses: mbarrier, TMA (cp.async.bulk.tensor, never with
-// cluster multicast), packed fp32x2 arithmetic and three-input min/max.
+// Thin wrappers over the sm_100a PTX this library uses: mbarrier, TMA (plain per-CTA cp.async.bulk.tensor
+// loads only), packed fp32x2 arithmetic and three-input min/max.
 //
 // Every wait is bounded: a wait that runs out of attempts records a code in a device-side status word
 // and returns false, and callers unwind instead of spinning forever.
