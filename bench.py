@@ -367,6 +367,126 @@ def run_ours(args, wl):
         dist.destroy_process_group()
 
 
+def run_apsp(args, wl):
+    """APSP workloads: one step = one squaring D <- min(D, D (x) D) of the sharded solve (cuasr_b200/apsp.py);
+    the line also carries the whole solve (ceil(log2 n) squarings) in seconds."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from cuasr_b200 import DType, Layout, Op, device_status, launch_count
+    from cuasr_b200.apsp import CudaBackend, ShardedSquaring
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n = wl.n
+    squarings = ShardedSquaring.squarings_needed(n)
+    backend = CudaBackend(n, rank, world, dev, mode=args.exchange)
+    graph = wl.operand("A", dev)
+    backend.load(0, graph)
+    solver = ShardedSquaring(n, rank, world, backend)
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        solver.step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = launch_count()
+    before_last = None
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        ev0.record(stream)
+        for _ in range(args.steps):
+            solver.step()
+        ev1.record(stream)
+        barrier()
+    launches = launch_count() - launches0
+    assert device_status() == 0
+    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t[0]) / args.steps
+    value = wl.ops / (ms_per_step * 1e-3) / 1e9
+
+    # ---- the whole solve end to end: adjacency matrix from pinned host memory, distances back ----
+    host_in = torch.empty(n * n, dtype=torch.float32).pin_memory()
+    host_in.copy_(graph)
+    host_out = torch.empty(n * n // world, dtype=torch.float32).pin_memory()
+    del graph
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    solver.cur, solver.nxt = 0, 1
+    backend.bufs[0].copy_(host_in, non_blocking=True)
+    for s in range(squarings):
+        if s == squarings - 1:
+            before_last = backend.matrix(solver.cur).clone()
+        solver.step()
+    mine = backend.matrix(solver.cur)[solver.c0 * n:(solver.c0 + solver.cols) * n]
+    host_out.copy_(mine, non_blocking=True)
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    solve_ms = float(t[0])
+
+    if rank == 0:
+        # 32 columns of the last squaring against the oracle fed that squaring's input
+        src = before_last.cpu().numpy()
+        blk = np.ascontiguousarray(src[: 32 * n])
+        want = np.empty(32 * n, np.float32)
+        fn = oracle.ref_srgemm if oracle.have_ref() else oracle.srgemm
+        col = Layout.COLUMN_MAJOR
+        t0 = time.perf_counter()
+        fn(Op.MINIMUM, Op.PLUS, DType.F32, (col, col, col), (n, 32, n), 0.0, src, n, blk, n, 0.0, blk, n, want, n,
+           np.float32(np.inf), 0)
+        cpu_sec = time.perf_counter() - t0
+        parity = bool(np.array_equal(host_out.numpy()[: 32 * n], want))
+        cores = oracle.max_threads(oracle.have_ref())
+        peaks, peak_kind = measured_peaks()
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        peak_tops = sms * 128 * 2 * peaks["sm_max_mhz"] * 1e6 / 1e12
+        achieved = (wl.ops / world) / (ms_per_step * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": "GOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(workload_config(wl), kernel="tma", exchange=args.exchange if world > 1 else "none",
+                           sharding=f"{n // world} columns of D per rank", l2="matrix (%d MiB) exceeds the 126 MB L2" % (n * n * 4 >> 20)),
+            "apsp": {"n": n, "squarings": squarings, "seconds": round(squarings * ms_per_step * 1e-3, 4),
+                     "seconds_end_to_end": round(solve_ms * 1e-3, 4)},
+            "e2e": {"value": round(squarings * wl.ops / (solve_ms * 1e-3) / 1e9, 2), "unit": "GOP/s",
+                    "h2d_bytes_per_step": n * n * 4 // squarings, "d2h_bytes_per_step": n * n * 4 // world // squarings,
+                    "ms_per_step": round(solve_ms / squarings, 3), "steps": squarings,
+                    "note": "one whole solve: adjacency matrix in from pinned host memory, all squarings, this rank's block of distances out"},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "CUDA cores (issue / register-file ports)", "achieved": round(achieved, 3),
+                         "peak": round(peak_tops, 2), "unit": "TOP/s", "frac": round(achieved / peak_tops, 4),
+                         "peak_source": f"{sms} SMs x 128 lanes x 2 x sm_max_mhz ({peak_kind})",
+                         "kernel_ms": round(ms_per_step, 4), "note": "step time includes the exchange", "traffic": None},
+            "cpu_baseline": {"value": round(2.0 * n * n * 32 / cpu_sec / 1e9, 3), "unit": "GOP/s", "cores": cores,
+                             "kind": "reference" if oracle.have_ref() else "port",
+                             "sample": f"32 columns of the last squaring ({2.0 * n * n * 32 / 1e9:.1f} GOP), all {cores} host threads"},
+            "parity_spot_check": parity,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     from cuasr_b200.workloads import WORKLOADS
 
@@ -385,7 +505,10 @@ def main():
         run_reference(args, wl)
     else:
         args.warmup = max(args.warmup, 3)
-        run_ours(args, wl)
+        if wl.fill == "apsp":
+            run_apsp(args, wl)
+        else:
+            run_ours(args, wl)
 
 
 if __name__ == "__main__":

@@ -54,6 +54,12 @@ class Workload:
             return fn(seed, count, self.lo, self.hi, device=device, start=start)
         if self.fill == "words":
             return datagen.words_u32(seed, count, device=device, start=start)
+        if self.fill == "apsp":
+            # A and B are the same matrix: the weighted adjacency matrix of the graph being solved
+            assert self.m == self.n == self.k and start % self.n == 0 and count % self.n == 0
+            return datagen.sparse_graph(SEED_A, self.n, self.density, self.absent(), dtype=torch.float32,
+                                        device=device, weight_lo=int(self.lo), weight_hi=int(self.hi),
+                                        integer_weights=True, row_start=start // self.n, rows=count // self.n)
         if self.fill == "graph":
             # square matrices only; storage line index = start // n works for either layout because the
             # generator is symmetric in how it treats rows and columns of the flat index
@@ -86,6 +92,12 @@ WORKLOADS = {w.name: w for w in [
              split_k_slices=32, description="config 3: 32 slices"),
     Workload("splitk_minplus_f32_s64", "minimum_plus", DType.F32, 256, 256, 1048576, (ROW, COL, ROW), "uniform", 0.0, 1.0,
              split_k_slices=64, description="config 3: 64 slices"),
+    Workload("apsp_16384", "minimum_plus", DType.F32, 16384, 16384, 16384, (COL, COL, COL), "apsp", 1.0, 100.0,
+             density=0.01, add_identity=math.inf,
+             description="config 4: APSP by repeated squaring, G(n = 16384, p = 0.01), integer weights 1..100 as fp32, "
+                         "14 squarings; one step = one squaring D <- min(D, D (x) D)"),
+    Workload("apsp_4096", "minimum_plus", DType.F32, 4096, 4096, 4096, (COL, COL, COL), "apsp", 1.0, 100.0,
+             density=0.01, add_identity=math.inf, description="config 4 at a quarter of the size (12 squarings)"),
     Workload("maxmin_f32_4096", "maximum_minimum", DType.F32, 4096, 4096, 4096, (COL, COL, COL), "uniform", 0.0, 1.0,
              add_identity=-math.inf, alpha=math.inf, beta=math.inf,
              description="config 5: max-min fp32, values uniform [0, 1)"),
