@@ -148,7 +148,7 @@ def sample_lines(wl, target_gop: float = 9.0) -> int:
 def run_reference(args, wl):
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    lines = sample_lines(wl)
+    lines = sample_lines(wl, 40.0)
     gops, kind, cores, sec, _ = cpu_run(wl, lines, repeats=args.steps, warmup=args.warmup)
     total_lines = wl.n if int(wl.layouts[2]) == 0 else wl.m
     sample = (f"first {lines} storage lines of D of the {wl.m}x{wl.n}x{wl.k} problem per step "
@@ -328,7 +328,7 @@ def run_ours(args, wl):
             parity = bool(np.array_equal(got, want))
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            lines = sample_lines(wl)
+            lines = sample_lines(wl, 400.0)     # about ten seconds of host work
             gops, kind, cores, sec, _ = cpu_run(wl, lines)
             cpu = {"value": round(gops, 3), "unit": "GOP/s", "cores": cores, "kind": kind,
                    "sample": f"first {lines} storage lines of D, one pass ({sec:.1f} s), all {cores} host threads"}
