@@ -87,6 +87,7 @@ class CudaBackend:
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         col = Layout.COLUMN_MAJOR
         self.op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, col, col, col, add_identity=self.inf)
+        self.workspace = None     # optional load-balancing scratch of the SRGEMM, sized on first use
         self.launches = 0
 
     # -- data ---------------------------------------------------------------------------------------------
@@ -105,7 +106,10 @@ class CudaBackend:
         args = self.Arguments((n, cols, n), (src, n), (src.data_ptr() + off, n), (src.data_ptr() + off, n),
                               (dst.data_ptr() + off, n), (0.0, 0.0))
         stream = self.torch.cuda.current_stream(self.device)
-        st = self.op.initialize(args, None, stream)
+        if self.workspace is None:
+            need = self.op.get_balance_workspace_size(args)
+            self.workspace = self.torch.empty(max(need, 1), dtype=self.torch.uint8, device=self.device)
+        st = self.op.initialize(args, self.workspace, stream)
         if st != self.Status.kSuccess:
             raise RuntimeError(f"SRGEMM rejected the squaring step: {st!r}")
         if self.world > 1 and self.mode == "push":

@@ -189,13 +189,47 @@ int validate(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Workspace layout for a split over `slices`: [tickets: one u32 per 128 x 128 tile, padded to 256 B]
-// [partials: slices * m * n elements].
+size_t tile_count(const cuasr_b200_args_t& args) {
+  return static_cast<size_t>((args.m + kTileM - 1) / kTileM) * ((args.n + kTileN - 1) / kTileN);
+}
+size_t ticket_bytes_for(const cuasr_b200_args_t& args) { return align_up(tile_count(args) * sizeof(unsigned int), 256); }
+
+// Scratch layout: [tickets: one u32 per 128 x 128 tile, padded to 256 B][partials: one full 128 x 128 block per
+// (split tile, slice)].  With every tile split (explicit split-K) that is tiles * slices blocks, which also
+// covers the slices * m * n elements the fallback kernel needs.
 size_t splitk_workspace_bytes(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args) {
   if (args.split_k_slices <= 1) return 0;
   const size_t es = desc.dtype == CUASR_F64 ? 8 : 4;
-  const size_t tiles = static_cast<size_t>((args.m + kTileM - 1) / kTileM + 1) * ((args.n + kTileN - 1) / kTileN + 1);
-  return align_up(tiles * sizeof(unsigned int), 256) + es * static_cast<size_t>(args.m) * args.n * args.split_k_slices;
+  return ticket_bytes_for(args) + es * tile_count(args) * kTileM * kTileN * args.split_k_slices;
+}
+
+// Load balancing of a launch that was not asked to split K: the tiles of the last, partial wave are cut along K
+// so that their pieces fill the SMs.  Returns the number of pieces (1 = leave the launch alone) and the number of
+// tiles that stay whole.
+struct BalancePlan {
+  int whole_tiles;
+  int pieces;
+};
+BalancePlan balance_plan(long long tiles, int sms, int k_tiles) {
+  BalancePlan plan{static_cast<int>(tiles), 1};
+  if (sms <= 0 || tiles <= 0) return plan;
+  const long long rem = tiles % sms;
+  if (rem == 0) return plan;
+  double best = 1.0;    // time of the last wave in units of one whole tile
+  const int max_pieces = k_tiles / 4 < 16 ? k_tiles / 4 : 16;
+  for (int s = 2; s <= max_pieces; ++s) {
+    const double t = static_cast<double>((rem * s + sms - 1) / sms) / s + 0.02 * s;   // + a little per piece for the fold
+    if (t < best - 0.05) { best = t; plan.pieces = s; }
+  }
+  if (plan.pieces > 1) plan.whole_tiles = static_cast<int>(tiles - rem);
+  return plan;
+}
+size_t balance_workspace_bytes(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int sms) {
+  const size_t es = desc.dtype == CUASR_F64 ? 8 : 4;
+  const int tk = kTileKBytes / static_cast<int>(es);
+  const BalancePlan plan = balance_plan(static_cast<long long>(tile_count(args)), sms, (args.k + tk - 1) / tk);
+  if (plan.pieces <= 1) return 0;
+  return ticket_bytes_for(args) + es * (tile_count(args) - plan.whole_tiles) * kTileM * kTileN * plan.pieces;
 }
 
 // Dispatch over rings.  X(ADD, MUL) is expanded for each ring the element type supports.
@@ -235,12 +269,20 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
   // split-K scratch
   unsigned int* tickets = nullptr;
   T* partial = nullptr;
+  BalancePlan plan{static_cast<int>(tile_count(args)), 1};
   if (slices > 1) {
     const size_t need = splitk_workspace_bytes(desc, args);
     if (args.workspace == nullptr) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
     if (args.workspace_bytes < need) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
-    const size_t tiles = static_cast<size_t>((args.m + kTileM - 1) / kTileM + 1) * ((args.n + kTileN - 1) / kTileN + 1);
-    const size_t ticket_bytes = align_up(tiles * sizeof(unsigned int), 256);
+    plan = BalancePlan{0, slices};
+  } else if (args.workspace != nullptr) {
+    // an optional workspace on an unsplit launch buys load balancing, if it is large enough for the plan
+    constexpr int tk = kTileKBytes / sizeof(T);
+    const BalancePlan wish = balance_plan(static_cast<long long>(tile_count(args)), dev->sms, (args.k + tk - 1) / tk);
+    if (wish.pieces > 1 && args.workspace_bytes >= balance_workspace_bytes(desc, args, dev->sms)) plan = wish;
+  }
+  if (plan.pieces > 1) {
+    const size_t ticket_bytes = ticket_bytes_for(args);
     tickets = static_cast<unsigned int*>(args.workspace);
     partial = reinterpret_cast<T*>(static_cast<char*>(args.workspace) + ticket_bytes);
     // same role as the semaphore memset of device/srgemm.h:253-259
@@ -283,11 +325,13 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
       tp.vector_epilogue = vec;
       tp.tiles_m = (p.m + kTileM - 1) / kTileM; tp.tiles_n = (p.n + kTileN - 1) / kTileN;
       tp.status = dev->status;
-      tp.slices = slices;
+      tp.whole_tiles = plan.whole_tiles;
+      tp.slices = plan.pieces;
       const int k_tiles = (p.k + TK - 1) / TK;
-      tp.k_tiles_per_slice = (k_tiles + slices - 1) / slices;
+      tp.k_tiles_per_slice = (k_tiles + plan.pieces - 1) / plan.pieces;
       tp.partial = partial; tp.tickets = tickets;
-      const long long work = static_cast<long long>(tp.tiles_m) * tp.tiles_n * slices;
+      const long long all_tiles = static_cast<long long>(tp.tiles_m) * tp.tiles_n;
+      const long long work = plan.whole_tiles + (all_tiles - plan.whole_tiles) * plan.pieces;
       const int grid = static_cast<int>(work < dev->sms ? work : dev->sms);
 #define X(ADD, MUL)                                                                                       \
       if (!launched && desc.add_op == ADD && desc.mul_op == MUL) {                                        \
@@ -299,7 +343,7 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
       CUASR_FLOAT_RINGS(X)
       if constexpr (std::is_integral<T>::value) { CUASR_BIT_RINGS(X) }
 #undef X
-      if (launched) t_last_kernel = slices > 1 ? "tma_splitk" : "tma";
+      if (launched) t_last_kernel = slices > 1 ? "tma_splitk" : plan.pieces > 1 ? "tma_balanced" : "tma";
     }
   }
   if (!launched) {
@@ -396,6 +440,14 @@ size_t cuasr_b200_srgemm_workspace_size(const cuasr_b200_desc_t* desc, const cua
   if (desc == nullptr || args == nullptr) return 0;
   if (desc->split_k_serial && args->split_k_slices > 1) return splitk_workspace_bytes(*desc, *args);
   return 0;
+}
+
+size_t cuasr_b200_srgemm_balance_workspace_size(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+  if (desc == nullptr || args == nullptr || validate(desc, args) != CUASR_STATUS_SUCCESS) return 0;
+  if (args->split_k_slices > 1) return 0;
+  DeviceState* dev = nullptr;
+  if (!device_state(&dev)) return 0;
+  return balance_workspace_bytes(*desc, *args, dev->sms);
 }
 
 int cuasr_b200_srgemm(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {

@@ -63,12 +63,14 @@ struct TmaParams {
   int vector_epilogue;          // D, C and every extra_d are 16-byte aligned, ld * sizeof(T) % 16 == 0, N % EV == 0
   int tiles_m, tiles_n;
   unsigned int* status;         // device status word (see DeviceStatus)
-  // split-K (slices > 1): slice z handles K tiles [z * k_tiles_per_slice, ...), the last slice takes the
-  // rest; raw accumulators go to partial + z * M * N (row-major, ld = N).  tickets[tile] counts the
-  // slices of an output tile that have been written; the CTA that draws the last ticket folds the
-  // slices in slice order and runs the epilogue, so nobody ever waits and the result does not depend
-  // on which CTA finishes last.  tickets must be zero at launch; the kernel leaves them zero.
-  int slices, k_tiles_per_slice;
+  // Work decomposition.  Tiles [0, whole_tiles) are computed whole by one CTA each.  Every later tile is cut
+  // along K into `slices` pieces: piece z handles K tiles [z * k_tiles_per_slice, ...), the last piece takes the
+  // rest, and writes its raw accumulators to partial + ((tile - whole_tiles) * slices + z) * 128 * 128 (a full
+  // 128 x 128 block, row-major).  tickets[tile - whole_tiles] counts the pieces written; the CTA that draws the
+  // last ticket folds the pieces in slice order and runs the epilogue, so nobody ever waits and the result does
+  // not depend on which CTA finishes last.  tickets must be zero at launch; the kernel leaves them zero.
+  // Explicit split-K is whole_tiles = 0; a balanced launch splits only the tiles of the last, partial wave.
+  int whole_tiles, slices, k_tiles_per_slice;
   T* partial;
   unsigned int* tickets;
 };
@@ -97,6 +99,20 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   const int width = min(kBand, tiles_n - band * kBand);
   tm = in_band / width;
   tn = band * kBand + in_band % width;
+}
+
+// Work item w of a launch -> (tile, K piece z, number of pieces of that tile).
+__device__ __forceinline__ void decode_work(int w, int num_tiles, int whole_tiles, int slices, int& tile, int& z,
+                                            int& pieces) {
+  if (w < whole_tiles) {
+    tile = w; z = 0; pieces = 1;
+  } else {
+    const int tail = num_tiles - whole_tiles;
+    const int v = w - whole_tiles;
+    z = v / tail;
+    tile = whole_tiles + (v - z * tail);
+    pieces = slices;
+  }
 }
 
 template <typename RingT, bool kAK, bool kBK>
@@ -128,7 +144,7 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   const int k_tiles_total = (p.K + TK - 1) / TK;
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int num_work = num_tiles * p.slices;
+  const int num_work = p.whole_tiles + (num_tiles - p.whole_tiles) * p.slices;
 
   if (warp >= kConsumerWarps) {
     // ---------------------------------------------------------------- producer
@@ -138,11 +154,11 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       prefetch_tensormap(&map_b);
       uint32_t it = 0;  // running K-tile counter across all work items: stage = it % kStages
       for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
-        const int z = w / num_tiles;
-        int tm, tn;
-        tile_coords(w - z * num_tiles, p.tiles_m, p.tiles_n, tm, tn);
-        const int kt_begin = z * p.k_tiles_per_slice;
-        const int kt_end = (z == p.slices - 1) ? k_tiles_total : min(k_tiles_total, kt_begin + p.k_tiles_per_slice);
+        int tile, z, pieces, tm, tn;
+        decode_work(w, num_tiles, p.whole_tiles, p.slices, tile, z, pieces);
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int kt_begin = pieces == 1 ? 0 : z * p.k_tiles_per_slice;
+        const int kt_end = (z == pieces - 1) ? k_tiles_total : min(k_tiles_total, kt_begin + p.k_tiles_per_slice);
         for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
           const int s = it % kStages;
           const uint32_t round = it / kStages;
@@ -183,11 +199,11 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   uint32_t it = 0;
   for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
-    const int z = w / num_tiles;
-    int tm, tn;
-    tile_coords(w - z * num_tiles, p.tiles_m, p.tiles_n, tm, tn);
-    const int kt_begin = z * p.k_tiles_per_slice;
-    const int kt_end = (z == p.slices - 1) ? k_tiles_total : min(k_tiles_total, kt_begin + p.k_tiles_per_slice);
+    int tile, z, pieces, tm, tn;
+    decode_work(w, num_tiles, p.whole_tiles, p.slices, tile, z, pieces);
+    tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+    const int kt_begin = pieces == 1 ? 0 : z * p.k_tiles_per_slice;
+    const int kt_end = (z == pieces - 1) ? k_tiles_total : min(k_tiles_total, kt_begin + p.k_tiles_per_slice);
 
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -289,49 +305,55 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
     // ---------------------------------------------------------------- epilogue
     const int m_base = tm * kTileM + wm * 64, n_base = tn * kTileN + wn * 32;
-    if (p.slices > 1) {
-      const int tile = w - z * num_tiles;
-      T* part = p.partial + (long long)z * p.M * p.N;
+    if (pieces > 1) {
+      // A piece of a split tile: park the raw accumulators in the tile's scratch block, in "fragment order"
+      // ([16 vectors][256 consumer threads][16 bytes], so that every access is a coalesced 16-byte vector and the
+      // thread that folds reads exactly the layout it would have written), then take a ticket.
+      constexpr int kVecPerThread = 64 / EV;
+      const int split = tile - p.whole_tiles;                     // index among the split tiles
+      T* block = p.partial + (long long)split * pieces * (kTileM * kTileN);
+      uint4* mine = reinterpret_cast<uint4*>(block + (long long)z * (kTileM * kTileN)) + threadIdx.x;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int m = m_base + row_of(i);
-        if (m >= p.M) continue;
+      for (int v = 0; v < kVecPerThread; ++v) {
+        alignas(16) T tmp[EV];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int n = n_base + col_of(j);
-          if (n < p.N) part[(long long)m * p.N + n] = acc[i][j];
-        }
+        for (int e = 0; e < EV; ++e) tmp[e] = acc[(v * EV + e) / 8][(v * EV + e) % 8];
+        mine[v * (kConsumerWarps * 32)] = *reinterpret_cast<const uint4*>(tmp);
       }
-      // publish this slice, then find out whether it completed the tile
       __threadfence();
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-      if (threadIdx.x == 0) *ticket_smem = atomicAdd(&p.tickets[tile], 1u);
+      if (threadIdx.x == 0) *ticket_smem = atomicAdd(&p.tickets[split], 1u);
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-      const bool last = (*ticket_smem == (unsigned)p.slices - 1);
+      const bool last = (*ticket_smem == (unsigned)pieces - 1);
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-      if (last) {
-        __threadfence();
-        if (threadIdx.x == 0) p.tickets[tile] = 0;
+      if (!last) continue;
+      // This CTA completed the tile: fold all pieces in slice order (a fixed order, whoever comes last), then
+      // fall through to the ordinary epilogue with the folded accumulators.
+      __threadfence();
+      if (threadIdx.x == 0) p.tickets[split] = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int m = m_base + row_of(i);
-          if (m >= p.M) continue;
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int n = n_base + col_of(j);
-            if (n >= p.N) continue;
-            T r = p.add_identity;
-            for (int zz = 0; zz < p.slices; ++zz)
-              r = RingT::add(__ldcg(p.partial + ((long long)zz * p.M + m) * p.N + n), r);
-            T v = RingT::mul(p.alpha, r);
-            if (p.read_c) v = RingT::add(v, RingT::mul(p.beta, p.C[(long long)m * p.ldc + n]));
-            const long long off = (long long)m * p.ldd + n;
-            p.D[off] = v;
-            for (int x = 0; x < p.n_extra; ++x) p.extra_d[x][off] = v;
+        for (int j = 0; j < 8; ++j) acc[i][j] = p.add_identity;
+      for (int zz = 0; zz < pieces; ++zz) {
+        const uint4* theirs = reinterpret_cast<const uint4*>(block + (long long)zz * (kTileM * kTileN)) + threadIdx.x;
+        uint4 raw[kVecPerThread];
+#pragma unroll
+        for (int v = 0; v < kVecPerThread; ++v) raw[v] = __ldcg(theirs + v * (kConsumerWarps * 32));
+#pragma unroll
+        for (int v = 0; v < kVecPerThread; ++v) {
+          alignas(16) T tmp[EV];
+          *reinterpret_cast<uint4*>(tmp) = raw[v];
+#pragma unroll
+          for (int e = 0; e < EV; ++e) {
+            T& a = acc[(v * EV + e) / 8][(v * EV + e) % 8];
+            a = RingT::add(tmp[e], a);
           }
         }
       }
-    } else if (p.vector_epilogue) {
+    }
+    if (p.vector_epilogue) {
+
       // Coalesced path: the warp's 64 x 32 block goes through its private staging area (rows of 32
       // elements, the 16-byte column groups XOR-swizzled by row & 7), then every lane handles 16 bytes of
       // a row: C is read, the epilogue applied and the vector stored to D and to every extra copy.

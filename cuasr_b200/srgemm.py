@@ -107,6 +107,11 @@ class _Operator:
     def get_workspace_size(self, args: Arguments) -> int:
         return int(self._fn("_workspace_size")(ctypes.byref(self._desc), ctypes.byref(self._pack(args))))
 
+    def get_balance_workspace_size(self, args: Arguments) -> int:
+        """Bytes of OPTIONAL workspace that let an unsplit launch balance its last wave over all SMs (0 = no gain)."""
+        return int(self._lib.cuasr_b200_srgemm_balance_workspace_size(ctypes.byref(self._desc),
+                                                                      ctypes.byref(self._pack(args))))
+
     def initialize(self, args: Arguments, workspace=None, stream=None, workspace_bytes: int = 0) -> Status:
         packed = self._pack(args, workspace, workspace_bytes, stream)
         status = Status(self._fn("_can_implement")(ctypes.byref(self._desc), ctypes.byref(packed)))

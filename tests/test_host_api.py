@@ -1,0 +1,80 @@
+"""Host-side logic of the C ABI that needs no GPU: argument validation, status codes and workspace sizes, called
+through the library with made-up (never dereferenced) pointers."""
+import numpy as np
+
+from cuasr_b200 import Arguments, DType, Layout, Op, Srgemm, SrgemmSplitKParallel, Status, annihilator, identity
+
+COL, ROW = Layout.COLUMN_MAJOR, Layout.ROW_MAJOR
+P = 0x10000  # a fake, 16-byte aligned device address
+
+
+def args(m=256, n=256, k=256, lda=256, ldb=256, ldc=256, ldd=256, a=P, b=P, c=P, d=P, slices=1, epilogue=(0.0, 0.0)):
+    return Arguments((m, n, k), (a, lda), (b, ldb), (c, ldc), (d, ldd), epilogue, slices)
+
+
+def test_can_implement_follows_the_reference_rules():
+    op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL)
+    assert op.can_implement(args()) == Status.kSuccess
+    assert op.can_implement(args(slices=2)) == Status.kErrorInvalidProblem          # device/srgemm.h:198-200
+    assert op.can_implement(args(m=0)) == Status.kErrorInvalidProblem
+    assert op.can_implement(args(lda=100)) == Status.kErrorInvalidProblem
+    assert op.can_implement(args(a=P + 2)) == Status.kErrorMisalignedOperand
+    assert op.can_implement(args(a=None)) == Status.kErrorInvalidProblem
+    serial = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL, split_k_serial=True)
+    assert serial.can_implement(args(slices=8)) == Status.kSuccess
+    assert SrgemmSplitKParallel(Op.MINIMUM, Op.PLUS, DType.F32, ROW, COL, ROW).can_implement(args(slices=8)) \
+        == Status.kSuccess
+
+
+def test_layout_decides_the_minimum_leading_dimension():
+    op = Srgemm(Op.PLUS, Op.MULTIPLIES, DType.F64, ROW, COL, ROW)
+    # A is 100 x 300 row-major (ld >= 300), B is 300 x 50 column-major (ld >= 300), C is 100 x 50 row-major (ld >= 50)
+    ok = args(m=100, n=50, k=300, lda=300, ldb=300, ldc=50, ldd=50, epilogue=(1.0, 0.0))
+    assert op.can_implement(ok) == Status.kSuccess
+    assert op.can_implement(args(m=100, n=50, k=300, lda=299, ldb=300, ldc=50, ldd=50)) == Status.kErrorInvalidProblem
+    assert op.can_implement(args(m=100, n=50, k=300, lda=300, ldb=300, ldc=50, ldd=49)) == Status.kErrorInvalidProblem
+    assert op.can_implement(args(m=100, n=50, k=300, lda=300, ldb=300, ldc=50, ldd=50, d=P + 4)) \
+        == Status.kErrorMisalignedOperand                                              # 8-byte elements
+
+
+def test_unsupported_combinations():
+    assert Srgemm(Op.BIT_XOR, Op.BIT_AND, DType.F32, COL, COL, COL).can_implement(args()) == Status.kErrorNotSupported
+    assert Srgemm(Op.PLUS, Op.PLUS, DType.F32, COL, COL, COL).can_implement(args()) == Status.kErrorNotSupported
+    assert Srgemm(Op.BIT_XOR, Op.BIT_AND, DType.U32, COL, COL, COL).can_implement(args()) == Status.kSuccess
+
+
+def test_workspace_sizes():
+    unsplit = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL)
+    assert unsplit.get_workspace_size(args()) == 0                                      # device/srgemm.h:218-234
+    par = SrgemmSplitKParallel(Op.MINIMUM, Op.PLUS, DType.F32, ROW, COL, ROW)
+    a16 = args(m=256, n=256, k=1 << 20, lda=1 << 20, ldb=1 << 20, slices=16)
+    need = par.get_workspace_size(a16)
+    # at least what the reference asks for: sizeof(element) * M * N * slices (device/srgemm_splitk_parallel.h:226-235)
+    assert need >= 4 * 256 * 256 * 16
+    assert need <= 4 * 256 * 256 * 16 + 4096
+    assert par.get_workspace_size(args(m=256, n=256, k=1 << 20, lda=1 << 20, ldb=1 << 20, slices=32)) > need
+    f64 = SrgemmSplitKParallel(Op.MINIMUM, Op.PLUS, DType.F64, ROW, COL, ROW)
+    assert f64.get_workspace_size(a16) >= 2 * (need - 4096)
+    # ragged shapes are padded to whole 128 x 128 tiles
+    assert par.get_workspace_size(args(m=130, n=70, k=1000, lda=1000, ldb=1000, ldc=70, ldd=70, slices=3)) \
+        >= 4 * 2 * 1 * 128 * 128 * 3
+
+
+def test_reference_constants():
+    """functional.h:28-36: '+inf' is numeric_limits::max(), '-inf' is numeric_limits::min()."""
+    assert identity(Op.MINIMUM, DType.F32) == np.finfo(np.float32).max
+    assert identity(Op.MAXIMUM, DType.F32) == np.finfo(np.float32).tiny
+    assert identity(Op.MAXIMUM, DType.S32) == np.iinfo(np.int32).min
+    assert annihilator(Op.PLUS, DType.F64) == np.finfo(np.float64).max
+    assert identity(Op.MINIMUM, DType.F32, true_infinity=True) == np.inf
+    assert identity(Op.BIT_AND, DType.U32) == 0xFFFFFFFF and identity(Op.BIT_XOR, DType.U32) == 0
+    assert annihilator(Op.MULTIPLIES, DType.F32) == 0 and identity(Op.MULTIPLIES, DType.F32) == 1
+
+
+def test_run_before_initialize_and_update():
+    op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL)
+    assert op.run() == Status.kErrorInternal
+    assert op.update(args()) == Status.kErrorInternal
+    assert op.initialize(args(slices=2)) == Status.kErrorInvalidProblem
+    assert op.initialize(args()) == Status.kSuccess
+    assert op.update(args(a=P + 4096)) == Status.kSuccess

@@ -177,6 +177,46 @@ def test_split_k_equals_single_pass(cuda_device, ring, dt):
     assert device_status() == 0
 
 
+@pytest.mark.parametrize("ring,dt", [("minimum_plus", DType.F32), ("plus_multiplies", DType.F32),
+                                     ("maximum_plus", DType.F64), ("bit_xor_bit_and", DType.U32)])
+def test_balanced_launch_with_optional_workspace(cuda_device, ring, dt):
+    """An unsplit launch given the optional workspace cuts the tiles of its last wave along K; the result must
+    not change (integer-valued data, so plus-times is exact as well)."""
+    import torch
+    rng = np.random.default_rng(31)
+    for layouts in (util.ALL_LAYOUTS[0], util.ALL_LAYOUTS[5]):
+        for (m, n, k) in ((512, 512, 512), (640, 384, 2048), (1000, 264, 520)):
+            A, lda = util.make_matrix(rng, dt, layouts[0], m, k)
+            B, ldb = util.make_matrix(rng, dt, layouts[1], k, n)
+            C, ldc = util.make_matrix(rng, dt, layouts[2], m, n)
+            alpha, _ = util.default_scalars(ring, dt)
+            want = util.run_oracle(ring, dt, layouts, (m, n, k), alpha, A, lda, B, ldb, alpha, C, ldc)
+
+            def dev(x):
+                return torch.from_numpy(x.view(np.int32) if x.dtype == np.uint32 else x).cuda()
+            dA, dB, dC = dev(A), dev(B), dev(C)
+            dD = torch.zeros_like(dC)
+            op = Srgemm(*RINGS[ring], dt, *layouts)
+            args = Arguments((m, n, k), (dA, lda), (dB, ldb), (dC, ldc), (dD, ldc), (alpha, alpha))
+            assert op.get_workspace_size(args) == 0
+            need = op.get_balance_workspace_size(args)
+            assert need > 0, (m, n, k)
+            ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+            for _ in range(2):   # twice: the tickets must be left clean
+                assert op(args, ws) == Status.kSuccess
+                torch.cuda.synchronize()
+                assert op.last_kernel() == "tma_balanced"
+                got = dD.cpu().numpy()
+                got = got.view(np.uint32) if dt == DType.U32 else got
+                assert np.array_equal(got, want), (ring, layouts, m, n, k)
+            # a workspace that is too small is simply not used
+            small = torch.empty(256, dtype=torch.uint8, device="cuda")
+            assert op(args, small) == Status.kSuccess
+            torch.cuda.synchronize()
+            assert op.last_kernel() == "tma"
+    assert device_status() == 0
+
+
 def test_plus_times_tolerance(cuda_device):
     """Plus-times on non-integer data: the device fuses multiply-add and sums in a different order, so the
     check is |got - want| <= 8 K eps (|A| |B|)_ij."""
