@@ -181,8 +181,19 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const int wm = warp / 4, wn = warp % 4;        // 2 x 4 warps
   const int lr = lane / 4, lc = lane % 4;        // 8 x 4 lanes
   // Row i (0..7) of this lane inside the warp's 64 rows; column j (0..7) inside the warp's 32 columns.
-  auto row_of = [&](int i) { return kAK ? (lr + 8 * i) : (EV * lr + (i % EV) + 8 * EV * (i / EV)); };
-  auto col_of = [&](int j) { return kBK ? (lc + 4 * j) : (EV * lc + (j % EV) + 4 * EV * (j / EV)); };
+  // Plus-times fp64 runs on the tensor cores (DMMA): acc[mb][2 nb + e] is then element e of the lane's
+  // accumulator pair of the 8 x 8 block (mb, nb) of the warp tile; its row inside the block is lr, its column
+  // 2 lc + e.  Blocks fed from an MN-contiguous operand are interleaved in pairs (see the loaders below).
+  constexpr bool kDmma = std::is_same<T, double>::value && RingT::kAdd == CUASR_OP_PLUS &&
+                         RingT::kMul == CUASR_OP_MULTIPLIES;
+  auto row_of = [&](int i) {
+    if (kDmma) return kAK ? (8 * i + lr) : (16 * (i / 2) + 2 * lr + (i % 2));
+    return kAK ? (lr + 8 * i) : (EV * lr + (i % EV) + 8 * EV * (i / EV));
+  };
+  auto col_of = [&](int j) {
+    if (kDmma) return kBK ? (8 * (j / 2) + 2 * lc + (j % 2)) : (16 * (j / 4) + 4 * lc + 2 * (j % 2) + ((j / 2) % 2));
+    return kBK ? (lc + 4 * j) : (EV * lc + (j % EV) + 4 * EV * (j / EV));
+  };
 
   // Byte offset of this lane's first operand vector inside a stage; every other vector of the lane is a
   // compile-time constant away from it.
@@ -266,7 +277,70 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               acc[i][j] = RingT::mac2(acc[i][j], a[i][e], b[j][e], a[i][e + 1], b[j][e + 1]);
       };
 
-      if constexpr (sizeof(T) == 4) {
+      if constexpr (kDmma) {
+        // Tensor-core path.  The fp64 mma takes, per lane, A(row lr [+8], k slot lc [+4]) and B(k slot lc [+4], column lr).
+        // The contraction index may be permuted freely as long as A and B agree: within a group of 8 k the
+        // slot lc of step s (s = 0, 1) stands for k = 2 lc + s, so a K-contiguous operand delivers both steps of
+        // a block with one 16-byte load.  An MN-contiguous operand delivers two adjacent rows with one 16-byte
+        // load; they feed the two blocks of an interleaved pair (block rows 2 lr and 2 lr + 1).
+        static_assert(!kDmma || TK == 16, "two groups of 8 k per stage");
+        auto load_group = [&](double (&a)[8][2], double (&b)[4][2], int group) {
+          if (kAK) {
+            const uint32_t base = sa + (wm * 64 + lr) * 128 + ((((group * 4 + lc) ^ lr) & 7) << 4);
+#pragma unroll
+            for (int mb = 0; mb < 8; ++mb) lds16(base + mb * 1024, a[mb]);
+          } else {
+#pragma unroll
+            for (int sstep = 0; sstep < 2; ++sstep) {
+              const uint32_t base = sa + (group * 8 + 2 * lc + sstep) * (kTileM * 8) + (wm * 64 + 2 * lr) * 8;
+#pragma unroll
+              for (int pr = 0; pr < 4; ++pr) {
+                double v[2];
+                lds16(base + pr * 128, v);
+                a[2 * pr][sstep] = v[0];
+                a[2 * pr + 1][sstep] = v[1];
+              }
+            }
+          }
+          if (kBK) {
+            const uint32_t base = sb + (wn * 32 + lr) * 128 + ((((group * 4 + lc) ^ lr) & 7) << 4);
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb) lds16(base + nb * 1024, b[nb]);
+          } else {
+#pragma unroll
+            for (int sstep = 0; sstep < 2; ++sstep) {
+              const uint32_t base = sb + (group * 8 + 2 * lc + sstep) * (kTileN * 8) + (wn * 32 + 2 * lr) * 8;
+#pragma unroll
+              for (int pr = 0; pr < 2; ++pr) {
+                double v[2];
+                lds16(base + pr * 128, v);
+                b[2 * pr][sstep] = v[0];
+                b[2 * pr + 1][sstep] = v[1];
+              }
+            }
+          }
+        };
+        auto mma_group = [&](const double (&a)[8][2], const double (&b)[4][2]) {
+          // m16n8k8: rows lr and lr + 8 of the instruction are the two 8-row blocks 2 h and 2 h + 1, k slots lc and
+          // lc + 4 are the two steps of this group
+#pragma unroll
+          for (int h = 0; h < 4; ++h)
+#pragma unroll
+            for (int nb = 0; nb < 4; ++nb)
+              asm volatile(
+                  "mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                  "{%0, %1, %2, %3};"
+                  : "+d"(acc[2 * h][2 * nb]), "+d"(acc[2 * h][2 * nb + 1]), "+d"(acc[2 * h + 1][2 * nb]),
+                    "+d"(acc[2 * h + 1][2 * nb + 1])
+                  : "d"(a[2 * h][0]), "d"(a[2 * h + 1][0]), "d"(a[2 * h][1]), "d"(a[2 * h + 1][1]), "d"(b[nb][0]),
+                    "d"(b[nb][1]));
+        };
+        double a0[8][2], b0[4][2], a1[8][2], b1[4][2];
+        load_group(a0, b0, 0);
+        load_group(a1, b1, 1);
+        mma_group(a0, b0);
+        mma_group(a1, b1);
+      } else if constexpr (sizeof(T) == 4) {
         // 4-byte elements: operand fragments are double-buffered in registers (64 + 4 x 32 registers)
         T a0[8][EV], b0[8][EV], a1[8][EV], b1[8][EV];
         load_a(a0, 0);
@@ -279,11 +353,6 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           if (chunk + 2 < kChunks) {
             load_a(a0, chunk + 2);
             load_b(b0, chunk + 2);
-          } else {
-            // every load from this stage has been issued; the arrive below is a release, so those loads
-            // have read shared memory before the producer can see the stage as free
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[s]);
           }
           compute(a1, b1);
         }
@@ -294,13 +363,14 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         for (int chunk = 0; chunk < kChunks; ++chunk) {
           load_a(a0, chunk);
           load_b(b0, chunk);
-          if (chunk + 1 == kChunks) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[s]);
-          }
           compute(a0, b0);
         }
       }
+      // Release the stage only after the math that consumed its last fragments: every value loaded from it is
+      // then in registers for certain (a release placed right after the loads leaves the compiler free to sink
+      // not-yet-needed loads below it, and the refill would race with them).
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
 
     // ---------------------------------------------------------------- epilogue

@@ -51,7 +51,7 @@ def test_reference_grid(cuda_device, ring, dt):
     assert device_status() == 0
 
 
-@pytest.mark.parametrize("ring,dt", [(r, d) for r, d in util.ring_dtype_cases() if d in (DType.F32, DType.U32)])
+@pytest.mark.parametrize("ring,dt", [(r, d) for r, d in util.ring_dtype_cases() if d in (DType.F32, DType.F64, DType.U32)])
 def test_tma_kernel_ragged_but_aligned(cuda_device, ring, dt):
     """16-byte aligned operands take the TMA kernel; M, N, K tails are not multiples of the tile."""
     from cuasr_b200.srgemm import _lib
@@ -64,8 +64,8 @@ def test_tma_kernel_ragged_but_aligned(cuda_device, ring, dt):
     assert device_status() == 0
     fast = {"minimum_plus", "maximum_plus", "minimum_maximum", "maximum_minimum", "plus_multiplies",
             "minimum_multiplies", "maximum_multiplies"}
-    if dt == DType.F32 and ring in fast:
-        assert kernels == {"tma"}, kernels
+    if dt in (DType.F32, DType.F64) and ring in fast:
+        assert kernels == {"tma"}, kernels     # plus-times fp64 is the tensor-core (DMMA) variant of that kernel
     if dt == DType.U32 and ring in ("bit_xor_bit_and", "bit_or_bit_and", "bit_xor_binary_and"):
         assert kernels == {"tma"}, kernels
 
