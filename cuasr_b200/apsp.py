@@ -147,3 +147,114 @@ def random_graph(n: int, p: float, seed: int, device, absent: float = math.inf, 
     start, count = rows
     return datagen.sparse_graph(seed, n, p, absent, dtype=torch.float32, device=device, weight_lo=1, weight_hi=100,
                                 integer_weights=True, row_start=start, rows=count)
+
+
+class BlockedFloydWarshall:
+    """All-pairs shortest paths by the three-phase blocked Floyd-Warshall scheme on top of the same min-plus
+    SRGEMM (its epilogue (+) with C is what the reference's README.md:338-342 positions for exactly this): 2 n^3
+    semiring operations in total instead of 2 n^3 log2(n) for repeated squaring.
+
+    D is column-major, n x n; rank g of G owns n / G consecutive columns and stores only those.  For every block
+    K = [kb * b, (kb + 1) * b) of vertices:
+      1. the rank that owns columns K closes the diagonal block (paths inside K) by ceil(log2 b) squarings of it;
+      2. it updates the column panel  P_col = min(D[:, K], D[:, K] (x) D[K, K]*)  and every rank receives P_col
+         (pushed by that SRGEMM's epilogue into symmetric memory, or broadcast with NCCL); every rank updates its
+         piece of the row panel  P_row = min(D[K, mine], D[K, K]* (x) D[K, mine]);
+      3. every rank updates its columns in place:  D[:, mine] = min(D[:, mine], P_col (x) P_row).
+    Panels are computed out of place, so no SRGEMM reads memory another CTA of the same launch writes.  With
+    integer edge weights every sum is exact and the result equals repeated squaring bit for bit; with general
+    floating-point weights the two orders of summation may round differently.
+    """
+
+    def __init__(self, n: int, block: int, rank: int, world: int, device, mode: str = "push", group=None):
+        import torch
+        import torch.distributed as dist
+
+        from .srgemm import Arguments, Srgemm, Status
+
+        if n % world or (n // world) % block:
+            raise ValueError(f"block size {block} must divide the {n // max(world, 1)} columns each rank owns")
+        if mode not in ("push", "allgather"):
+            raise ValueError(mode)
+        self.n, self.b, self.rank, self.world, self.device, self.mode = n, block, rank, world, device, mode
+        self.torch, self.dist, self.group = torch, dist, group
+        self.Status, self.Arguments = Status, Arguments
+        self.cols = n // world
+        self.c0 = rank * self.cols
+        f32 = torch.float32
+        self.D = torch.empty(n * self.cols, dtype=f32, device=device)          # my columns, ld = n
+        self.p_row = torch.empty(block * self.cols, dtype=f32, device=device)  # ld = block
+        self.diag = [torch.empty(block * block, dtype=f32, device=device) for _ in range(2)]
+        self.peer_pcol: List[List[int]] = [[], []]
+        if world > 1 and mode == "push":
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.p_col = [symm_mem.empty(n * block, dtype=f32, device=device) for _ in range(2)]
+            handles = [symm_mem.rendezvous(t, dist.group.WORLD if group is None else group) for t in self.p_col]
+            self._handles = handles
+            self.peer_pcol = [[int(p) for p in h.buffer_ptrs] for h in handles]
+        else:
+            self.p_col = [torch.empty(n * block, dtype=f32, device=device) for _ in range(2)]
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        col = Layout.COLUMN_MAJOR
+        self.op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, col, col, col, add_identity=math.inf)
+        self._workspaces = {}
+        self.launches = 0
+
+    def load_columns(self, flat) -> None:
+        """`flat`: this rank's n x cols block of the weighted adjacency matrix (column-major, diagonal 0)."""
+        self.D.copy_(flat)
+
+    def _srgemm(self, m, n, k, A, lda, B, ldb, C, ldc, D, ldd, extras=()):
+        """D = min(C, A (x) B); all arguments are device addresses."""
+        args = self.Arguments((m, n, k), (A, lda), (B, ldb), (C, ldc), (D, ldd), (0.0, 0.0))
+        key = (m, n, k)
+        if key not in self._workspaces:
+            need = self.op.get_balance_workspace_size(args)
+            self._workspaces[key] = self.torch.empty(max(need, 1), dtype=self.torch.uint8, device=self.device)
+        stream = self.torch.cuda.current_stream(self.device)
+        st = self.op.initialize(args, self._workspaces[key], stream)
+        if st == self.Status.kSuccess:
+            st = self.op.run_push(list(extras), stream) if extras else self.op.run(stream)
+        if st != self.Status.kSuccess:
+            raise RuntimeError(f"SRGEMM failed: {st!r}")
+        self.launches += 1
+
+    def solve(self) -> None:
+        n, b, es = self.n, self.b, 4
+        torch = self.torch
+        Dp = self.D.data_ptr()
+        squarings = max(1, math.ceil(math.log2(b)))
+        for kb in range(n // b):
+            k0 = kb * b
+            owner = k0 // self.cols
+            pc = self.p_col[kb % 2]
+            pcp = pc.data_ptr()
+            if self.rank == owner:
+                lc = k0 - self.c0                                   # first local column of block K
+                # phase 1: closure of the diagonal block by repeated squaring of a private copy
+                src = self.D.view(self.cols, n)[lc:lc + b, k0:k0 + b]
+                self.diag[0].view(b, b).copy_(src)
+                cur = 0
+                for _ in range(squarings):
+                    s, d = self.diag[cur].data_ptr(), self.diag[1 - cur].data_ptr()
+                    self._srgemm(b, b, b, s, b, s, b, s, b, d, b)
+                    cur = 1 - cur
+                star = self.diag[cur].data_ptr()
+                # phase 2, column panel: P_col = min(D[:, K], D[:, K] (x) D[K, K]*), delivered to every rank
+                panel = Dp + lc * n * es
+                extras = [p for r, p in enumerate(self.peer_pcol[kb % 2]) if r != self.rank]
+                self._srgemm(n, b, b, panel, n, star, b, panel, n, pcp, n, extras)
+            if self.world > 1:
+                if self.mode == "push":
+                    self.dist.all_reduce(self._flag, group=self.group)      # stream-ordered barrier
+                else:
+                    self.dist.broadcast(pc, src=owner, group=self.group)
+            # phase 2, my piece of the row panel: P_row = min(D[K, mine], D[K, K]* (x) D[K, mine]); D[K, K]* = P_col[K, :]
+            rows = Dp + k0 * es
+            self._srgemm(b, self.cols, b, pcp + k0 * es, n, rows, n, rows, n, self.p_row.data_ptr(), b)
+            # phase 3: D[:, mine] = min(D[:, mine], P_col (x) P_row), in place (C aliases D; the operands are copies)
+            self._srgemm(n, self.cols, b, pcp, n, self.p_row.data_ptr(), b, Dp, n, Dp, n)
+
+    def result_columns(self):
+        return self.D

@@ -96,6 +96,9 @@ WORKLOADS = {w.name: w for w in [
              density=0.01, add_identity=math.inf,
              description="config 4: APSP by repeated squaring, G(n = 16384, p = 0.01), integer weights 1..100 as fp32, "
                          "14 squarings; one step = one squaring D <- min(D, D (x) D)"),
+    Workload("apsp_fw_16384", "minimum_plus", DType.F32, 16384, 16384, 16384, (COL, COL, COL), "apsp", 1.0, 100.0,
+             density=0.01, add_identity=math.inf,
+             description="the graph of config 4 solved by blocked Floyd-Warshall on the same SRGEMM (one step = one solve)"),
     Workload("apsp_4096", "minimum_plus", DType.F32, 4096, 4096, 4096, (COL, COL, COL), "apsp", 1.0, 100.0,
              density=0.01, add_identity=math.inf, description="config 4 at a quarter of the size (12 squarings)"),
     Workload("maxmin_f32_4096", "maximum_minimum", DType.F32, 4096, 4096, 4096, (COL, COL, COL), "uniform", 0.0, 1.0,

@@ -8,7 +8,7 @@ import pytest
 
 import oracle
 from cuasr_b200 import DType, Layout, Op
-from cuasr_b200.apsp import CudaBackend, ShardedSquaring, random_graph
+from cuasr_b200.apsp import BlockedFloydWarshall, CudaBackend, ShardedSquaring, random_graph
 
 pytestmark = pytest.mark.gpu
 COL = Layout.COLUMN_MAJOR
@@ -68,6 +68,56 @@ def test_apsp_blocks_at_full_size_property(cuda_device):
         assert np.array_equal(got[blk], want), f"columns {c0}..{c0 + 31}"
     # squaring never lengthens a path
     assert bool((solver.result() <= before).all())
+
+
+def test_blocked_floyd_warshall_equals_repeated_squaring(cuda_device):
+    """Integer weights: both algorithms are exact, so the distances must be identical bit for bit."""
+    import torch
+    n, seed = 1024, 13
+    flat = random_graph(n, 0.01, seed, cuda_device)
+    want = cpu_apsp(flat.cpu().numpy(), n, ShardedSquaring.squarings_needed(n))
+    for block in (256, 512, 1024):
+        solver = BlockedFloydWarshall(n, block, 0, 1, cuda_device)
+        solver.load_columns(flat)
+        solver.solve()
+        torch.cuda.synchronize()
+        assert np.array_equal(solver.result_columns().cpu().numpy(), want), f"block {block}"
+
+
+def _fw_rank(rank, world, port, n, seed, mode, out):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    cols = n // world
+    solver = BlockedFloydWarshall(n, 128, rank, world, dev, mode=mode)
+    solver.load_columns(random_graph(n, 0.01, seed, dev, rows=(rank * cols, cols)))
+    solver.solve()
+    torch.cuda.synchronize()
+    out[(mode, rank)] = solver.result_columns().cpu().numpy()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["allgather", "push"])
+def test_multi_gpu_blocked_floyd_warshall(mode):
+    import torch
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    n, seed = 1024, 27
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = mp.Manager().dict()
+    mp.spawn(_fw_rank, args=(world, port, n, seed, mode, out), nprocs=world, join=True)
+    want = cpu_apsp(random_graph(n, 0.01, seed, "cpu").numpy(), n, ShardedSquaring.squarings_needed(n))
+    cols = n // world
+    for rank in range(world):
+        assert np.array_equal(out[(mode, rank)], want[rank * cols * n:(rank + 1) * cols * n]), f"{mode}: rank {rank}"
 
 
 def _rank(rank, world, port, n, seed, mode, out):
