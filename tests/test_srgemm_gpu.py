@@ -217,6 +217,32 @@ def test_balanced_launch_with_optional_workspace(cuda_device, ring, dt):
     assert device_status() == 0
 
 
+@pytest.mark.parametrize("layouts", [(COL, COL, COL), (ROW, COL, ROW), (ROW, ROW, ROW), (COL, ROW, COL)])
+def test_host_buffer_pipeline_equals_one_shot(cuda_device, layouts):
+    """HostSrgemm (pinned host operands, chunked and overlapped copies) gives exactly the one-shot result."""
+    import torch
+    from cuasr_b200 import HostSrgemm
+    rng = np.random.default_rng(77)
+    dt, ring = DType.F32, "minimum_plus"
+    m, n, k = 1024, 768, 640
+    A, lda = util.make_matrix(rng, dt, layouts[0], m, k)
+    B, ldb = util.make_matrix(rng, dt, layouts[1], k, n)
+    C, ldc = util.make_matrix(rng, dt, layouts[2], m, n)
+    want = util.run_oracle(ring, dt, layouts, (m, n, k), 0.0, A, lda, B, ldb, 0.0, C, ldc)
+    op = Srgemm(*RINGS[ring], dt, *layouts)
+    pipe = HostSrgemm(op, m, n, k, 0.0, 0.0, cuda_device, chunks=4)
+    hA, hB, hC = (torch.from_numpy(x).pin_memory() for x in (A, B, C))
+    hD = torch.empty(m * n, dtype=torch.float32).pin_memory()
+    for _ in range(2):
+        hD.zero_()
+        pipe(hA, hB, hC, hD)
+        torch.cuda.synchronize()
+        assert np.array_equal(hD.numpy(), want)
+    chunked = layouts in ((COL, COL, COL), (ROW, COL, ROW), (ROW, ROW, ROW))
+    assert pipe.chunks == (4 if chunked else 1)
+    assert device_status() == 0
+
+
 def test_plus_times_tolerance(cuda_device):
     """Plus-times on non-integer data: the device fuses multiply-add and sums in a different order, so the
     check is |got - want| <= 8 K eps (|A| |B|)_ij."""
