@@ -44,6 +44,8 @@ PROTOTYPES = {
     "cuasr_b200_srgemm_balance_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_push": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args), ctypes.c_int,
                                               ctypes.POINTER(ctypes.c_void_p)]),
+    "cuasr_b200_srgemm_path": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args), ctypes.c_void_p,
+                                              ctypes.c_int64, ctypes.c_int32]),
     "cuasr_b200_srgemm_splitk_can_implement": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_splitk_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_splitk": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),

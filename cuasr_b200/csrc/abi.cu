@@ -14,6 +14,7 @@
 
 #include "../../include/cuasr_b200.h"
 #include "srgemm_launch.h"
+#include "srgemm_path.cuh"
 
 namespace cuasr_b200 {
 namespace {
@@ -501,6 +502,47 @@ int cuasr_b200_srgemm_splitk_static(const cuasr_b200_desc_t* desc, const cuasr_b
   with_scratch.workspace = scratch;
   with_scratch.workspace_bytes = CUASR_B200_STATIC_SCRATCH_BYTES;
   return run(desc, &with_scratch, with_scratch.split_k_slices);
+}
+
+int cuasr_b200_srgemm_path(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args, int32_t* parent,
+                           int64_t ld_parent, int32_t k_offset) {
+  const int st = validate(desc, args);
+  if (st != CUASR_STATUS_SUCCESS) return st;
+  const bool minimize = desc->add_op == CUASR_OP_MINIMUM, maximize = desc->add_op == CUASR_OP_MAXIMUM;
+  if (!(minimize || maximize) || desc->mul_op != CUASR_OP_PLUS) return CUASR_STATUS_ERROR_NOT_SUPPORTED;
+  if (desc->dtype != CUASR_F32 && desc->dtype != CUASR_F64) return CUASR_STATUS_ERROR_INVALID_DATA_TYPE;
+  if (args->split_k_slices != 1) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (parent == nullptr || reinterpret_cast<uintptr_t>(parent) % 4 != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+  const bool row_c = desc->layout_c == CUASR_ROW_MAJOR;
+  if (ld_parent < (row_c ? args->n : args->m)) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  auto fill = [&](auto* pp) {
+    pp->M = args->m; pp->N = args->n; pp->K = args->k;
+    const bool row_a = desc->layout_a == CUASR_ROW_MAJOR, row_b = desc->layout_b == CUASR_ROW_MAJOR;
+    pp->a_row = row_a ? args->lda : 1; pp->a_col = row_a ? 1 : args->lda;
+    pp->b_row = row_b ? args->ldb : 1; pp->b_col = row_b ? 1 : args->ldb;
+    pp->d_row = row_c ? args->ldd : 1; pp->d_col = row_c ? 1 : args->ldd;
+    pp->p_row = row_c ? ld_parent : 1; pp->p_col = row_c ? 1 : ld_parent;
+    pp->parent = parent; pp->k_offset = k_offset;
+  };
+  cudaStream_t stream = static_cast<cudaStream_t>(args->stream);
+  cudaError_t err;
+  if (desc->dtype == CUASR_F32) {
+    PathParams<float> pp;
+    fill(&pp);
+    pp.A = static_cast<const float*>(args->A); pp.B = static_cast<const float*>(args->B);
+    pp.dist = static_cast<float*>(args->D);
+    err = launch_path<float>(pp, maximize, stream);
+  } else {
+    PathParams<double> pp;
+    fill(&pp);
+    pp.A = static_cast<const double*>(args->A); pp.B = static_cast<const double*>(args->B);
+    pp.dist = static_cast<double*>(args->D);
+    err = launch_path<double>(pp, maximize, stream);
+  }
+  if (err != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+  g_launches.fetch_add(1);
+  t_last_kernel = "path";
+  return CUASR_STATUS_SUCCESS;
 }
 
 int cuasr_b200_device_status(void* stream) {

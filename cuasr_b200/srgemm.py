@@ -173,6 +173,17 @@ class SrgemmSplitKParallel(_Operator):
     _splitk_parallel = True
 
 
+def srgemm_path(operator: _Operator, problem_size, ref_A, ref_B, ref_dist, ref_parent, k_offset: int = 0,
+                stream=None) -> Status:
+    """dist <- min/max(dist, A (x) B) in place with the winning contraction index recorded in `parent` (int32, same
+    layout as dist): cuasr_b200_srgemm_path.  `operator` supplies ring (min-plus or max-plus), type and layouts."""
+    args = Arguments(problem_size, ref_A, ref_B, ref_dist, ref_dist)
+    packed = operator._pack(args, None, 0, stream)
+    lib = _lib.load()
+    return Status(lib.cuasr_b200_srgemm_path(ctypes.byref(operator._desc), ctypes.byref(packed), _ptr(ref_parent[0]),
+                                             int(ref_parent[1]), int(k_offset)))
+
+
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024 + 4096
 
 

@@ -98,6 +98,16 @@ CUASR_B200_API size_t cuasr_b200_srgemm_balance_workspace_size(const cuasr_b200_
 CUASR_B200_API int cuasr_b200_srgemm_push(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args, int n_extra,
                                           void *const *extra_d);
 
+/* Path-tracking tropical product, in place: D[m, n] <- min (or max) of D[m, n] and A[m, k] + B[k, n] over k, and
+ * parent[m, n] <- k_offset + the first k whose product was strictly better than everything before it (parent is
+ * left alone where nothing improved).  Device form of the reference's legacy CPU routine cpu_fwgemm_naive
+ * (test/regress/include/fwgpu/cpu_srgemm.hpp:20-48), generalised to both layouts, M x N x K and max-plus.
+ * desc: add_op MINIMUM or MAXIMUM, mul_op PLUS, dtype F32 or F64.  args: A, B, D (= the distances, read and
+ * written; C, alpha, beta, workspace are ignored), split_k_slices = 1.  parent has D's layout, leading dimension
+ * ld_parent, 32-bit signed entries. */
+CUASR_B200_API int cuasr_b200_srgemm_path(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args, int32_t *parent,
+                                          int64_t ld_parent, int32_t k_offset);
+
 /* SrgemmSplitKParallel::can_implement / get_workspace_size / operator()
  * (device/srgemm_splitk_parallel.h:220-235, :238-279, :333-348).  The reference needs
  * sizeof(element) * M * N * slices bytes of workspace and two launches; this library needs a little more

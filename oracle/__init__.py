@@ -72,3 +72,19 @@ def ref_srgemm(add_op, mul_op, dtype, layouts, mnk, alpha, A, lda, B, ldb, beta,
     _, fn = _load(REF_PATH, "cuasr_ref_srgemm")
     return _call(fn, add_op, mul_op, dtype, layouts, mnk, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd,
                  add_identity, nthreads)
+
+
+def srgemm_path(dtype, layouts, mnk, A, lda, B, ldb, dist, lddist, parent, ldparent, k_offset=0, maximize=False):
+    """In-place path-tracking tropical product on the CPU (cuasr_oracle_srgemm_path); returns (dist, parent)."""
+    lib, _ = _load(ORACLE_PATH, "cuasr_oracle_srgemm")
+    fn = lib.cuasr_oracle_srgemm_path
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int] * 7 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                        ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    assert parent.dtype == np.int32 and dist.flags["C_CONTIGUOUS"] and parent.flags["C_CONTIGUOUS"]
+    st = fn(int(dtype), int(layouts[0]), int(layouts[1]), int(layouts[2]), int(mnk[0]), int(mnk[1]), int(mnk[2]),
+            A.ctypes.data, int(lda), B.ctypes.data, int(ldb), dist.ctypes.data, int(lddist), parent.ctypes.data,
+            int(ldparent), int(k_offset), int(bool(maximize)))
+    if st != 0:
+        raise RuntimeError(f"oracle returned status {st}")
+    return dist, parent

@@ -186,3 +186,52 @@ int cuasr_oracle_max_threads(void) {
   return 1;
 #endif
 }
+
+/*
+ * Path-tracking tropical product: restatement of the reference's legacy CPU routine
+ *   test/regress/include/fwgpu/cpu_srgemm.hpp:20-48  (cpu_fwgemm_naive)
+ * for every (row, col): the running distance starts at dist[row, col], the running parent at parent[row, col];
+ * for k ascending, a product A[row, k] + B[k, col] that is STRICTLY better replaces the distance and sets the
+ * parent to k (so ties keep the earlier k, and an entry that is never improved keeps its old parent).
+ * Generalised from the reference's square, column-major, min-only form to M x N x K, both layouts, and max-plus;
+ * k_offset is added to the recorded index (for callers that work on a K-block of a larger product).
+ * Parity status: the reference holds no test or fixture for this routine (it is never called there), so the
+ * parent output is UNPINNED against the reference; the distance output is pinned through cuasr_oracle_srgemm.
+ */
+#define DEFINE_PATH(NAME, T)                                                                            \
+  static void NAME(int M, int N, int K, const T *A, int rmA, int lda, const T *B, int rmB, int ldb,     \
+                   T *dist, int rmC, int lddist, int32_t *parent, int ldparent, int k_offset, int maximize) { \
+    for (int row = 0; row < M; ++row) {                                                                 \
+      for (int col = 0; col < N; ++col) {                                                               \
+        T cur = AT(dist, rmC, lddist, row, col);                                                        \
+        int32_t par = AT(parent, rmC, ldparent, row, col);                                              \
+        for (int k = 0; k < K; ++k) {                                                                   \
+          T prod = (T)(AT(A, rmA, lda, row, k) + AT(B, rmB, ldb, k, col));                              \
+          if (maximize ? (cur < prod) : (prod < cur)) {                                                 \
+            cur = prod;                                                                                 \
+            par = k + k_offset;                                                                         \
+          }                                                                                             \
+        }                                                                                               \
+        AT(dist, rmC, lddist, row, col) = cur;                                                          \
+        AT(parent, rmC, ldparent, row, col) = par;                                                      \
+      }                                                                                                 \
+    }                                                                                                   \
+  }
+DEFINE_PATH(path_f32, float)
+DEFINE_PATH(path_f64, double)
+
+int cuasr_oracle_srgemm_path(int dtype, int layoutA, int layoutB, int layoutC, int M, int N, int K, const void *A,
+                             int lda, const void *B, int ldb, void *dist, int lddist, int32_t *parent,
+                             int ldparent, int k_offset, int maximize) {
+  if (M < 0 || N < 0 || K < 0) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  int ra = layoutA == CUASR_ROW_MAJOR, rb = layoutB == CUASR_ROW_MAJOR, rc = layoutC == CUASR_ROW_MAJOR;
+  if (dtype == CUASR_F32)
+    path_f32(M, N, K, (const float *)A, ra, lda, (const float *)B, rb, ldb, (float *)dist, rc, lddist, parent,
+             ldparent, k_offset, maximize);
+  else if (dtype == CUASR_F64)
+    path_f64(M, N, K, (const double *)A, ra, lda, (const double *)B, rb, ldb, (double *)dist, rc, lddist, parent,
+             ldparent, k_offset, maximize);
+  else
+    return CUASR_STATUS_ERROR_INVALID_DATA_TYPE;
+  return CUASR_STATUS_SUCCESS;
+}

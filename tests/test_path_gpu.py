@@ -1,0 +1,67 @@
+"""Path-tracking tropical product (cuasr_b200_srgemm_path) against the CPU restatement of the reference's
+cpu_fwgemm_naive (test/regress/include/fwgpu/cpu_srgemm.hpp:20-48)."""
+import numpy as np
+import pytest
+
+import oracle
+import util
+from cuasr_b200 import DType, Layout, Op, Srgemm, Status, device_status, srgemm_path
+from cuasr_b200.semiring import NUMPY_DTYPE
+
+COL, ROW = Layout.COLUMN_MAJOR, Layout.ROW_MAJOR
+
+
+def test_oracle_path_distances_equal_the_pinned_srgemm_oracle():
+    """The distance half of the path oracle is the min-plus SRGEMM with C = the old distances."""
+    rng = np.random.default_rng(3)
+    m, n, k = 37, 29, 41
+    A = rng.integers(0, 9, m * k).astype(np.float32)
+    B = rng.integers(0, 9, k * n).astype(np.float32)
+    C = rng.integers(0, 30, m * n).astype(np.float32)
+    want = util.run_oracle("minimum_plus", DType.F32, (COL, COL, COL), (m, n, k), 0.0, A, m, B, k, 0.0, C, m)
+    dist, parent = oracle.srgemm_path(DType.F32, (COL, COL, COL), (m, n, k), A, m, B, k, C.copy(), m,
+                                      np.full(m * n, -1, np.int32), m)
+    assert np.array_equal(dist, want)
+    # every recorded parent reproduces its distance, and it is the FIRST k that does
+    Am, Bm = A.reshape(k, m).T, B.reshape(n, k).T
+    P, Dm, Cm = parent.reshape(n, m).T, dist.reshape(n, m).T, C.reshape(n, m).T
+    for i in range(m):
+        for j in range(n):
+            if P[i, j] >= 0:
+                sums = Am[i, :] + Bm[:, j]
+                assert Dm[i, j] < Cm[i, j] and sums[P[i, j]] == Dm[i, j] and np.argmin(sums) == P[i, j]
+            else:
+                assert Dm[i, j] == Cm[i, j]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [DType.F32, DType.F64])
+@pytest.mark.parametrize("maximize", [False, True])
+def test_path_tracking_matches_oracle(cuda_device, dt, maximize):
+    import torch
+    rng = np.random.default_rng(19)
+    np_t = NUMPY_DTYPE[dt]
+    add_op = Op.MAXIMUM if maximize else Op.MINIMUM
+    for layouts in (util.ALL_LAYOUTS[0], util.ALL_LAYOUTS[3], util.ALL_LAYOUTS[5], util.ALL_LAYOUTS[6]):
+        for (m, n, k, integers) in ((1, 1, 1, True), (130, 67, 45, True), (257, 129, 100, False), (64, 64, 300, True)):
+            A, lda = util.make_matrix(rng, dt, layouts[0], m, k, util.extents(layouts[0], m, k)[0] + 3)
+            B, ldb = util.make_matrix(rng, dt, layouts[1], k, n, util.extents(layouts[1], k, n)[0] + 1)
+            D, ldd = util.make_matrix(rng, dt, layouts[2], m, n, util.extents(layouts[2], m, n)[0] + 2, lo=-4, hi=4)
+            if not integers:   # real values: ties are unlikely; integers: ties are the rule and test "first k wins"
+                A = (A + rng.random(A.size)).astype(np_t)
+                B = (B + rng.random(B.size)).astype(np_t)
+            parent = np.full(D.size, -7, np.int32)
+            want_d, want_p = oracle.srgemm_path(dt, layouts, (m, n, k), A, lda, B, ldb, D.copy(), ldd, parent.copy(), ldd,
+                                                k_offset=1000, maximize=maximize)
+            dA, dB, dD, dP = (torch.from_numpy(x).cuda() for x in (A, B, D, parent))
+            op = Srgemm(add_op, Op.PLUS, dt, *layouts)
+            st = srgemm_path(op, (m, n, k), (dA, lda), (dB, ldb), (dD, ldd), (dP, ldd), k_offset=1000)
+            assert st == Status.kSuccess
+            torch.cuda.synchronize()
+            assert np.array_equal(dD.cpu().numpy(), want_d), (layouts, m, n, k)
+            assert np.array_equal(dP.cpu().numpy(), want_p), (layouts, m, n, k)
+    assert device_status() == 0
+    bad = Srgemm(Op.PLUS, Op.MULTIPLIES, dt, COL, COL, COL)
+    x = torch.zeros(16, device="cuda", dtype=torch.float32 if dt == DType.F32 else torch.float64)
+    p = torch.zeros(16, device="cuda", dtype=torch.int32)
+    assert srgemm_path(bad, (4, 4, 4), (x, 4), (x, 4), (x, 4), (p, 4)) == Status.kErrorNotSupported
