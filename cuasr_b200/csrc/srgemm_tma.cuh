@@ -36,7 +36,7 @@ constexpr int kStages = 5;
 constexpr int kConsumerWarps = 8;
 constexpr int kProducerWarps = 4;                 // one warpgroup; only its first lane issues TMA
 constexpr int kTmaThreads = (kConsumerWarps + kProducerWarps) * 32;
-// Register budget per thread after the warpgroups re-balance with setmaxnreg: the two consumer warps and
+// Registers per thread after the warpgroups re-balance with setmaxnreg: the two consumer warps and
 // the one producer warp that share an SM sub-partition fit its 16384 registers (2 * 232 + 40 = 504 <= 512).
 constexpr int kConsumerRegs = 232;
 constexpr int kProducerRegs = 40;

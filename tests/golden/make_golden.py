@@ -1,5 +1,5 @@
 """Generates the golden fixtures of tests/golden/ from the REFERENCE checkout.  Run in a container that has
-the reference (default /root/reference) and oracle/_ref built (`make -C oracle ref`):
+a checkout of the reference (path as first argument, or $CUASR_REFERENCE) and oracle/_ref built (`make -C oracle ref`):
 
     python tests/golden/make_golden.py [/path/to/reference]
 
@@ -63,7 +63,7 @@ def host_outputs():
 
 
 def main():
-    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    reference = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CUASR_REFERENCE", "/root/reference")
     assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref"
     with open(os.path.join(HERE, "regress_known_answer.json"), "w") as f:
         json.dump(known_answer(reference), f, indent=1)
