@@ -87,6 +87,17 @@ struct Ring {
     }
   }
 
+  // fp32 rings whose two steps map onto ONE packed fp32x2 add/multiply and ONE three-input min/max.  Used where
+  // both operands deliver (k, k+1) pairs in adjacent registers (both K-contiguous in shared memory).
+  static constexpr bool kPackedPairs = std::is_same<T, float>::value &&
+                                       (ADD == CUASR_OP_MINIMUM || ADD == CUASR_OP_MAXIMUM) &&
+                                       (MUL == CUASR_OP_PLUS || MUL == CUASR_OP_MULTIPLIES);
+  static __device__ __forceinline__ float mac_packed(float acc, uint64_t a, uint64_t b) {
+    float p0, p1;
+    unpack2(MUL == CUASR_OP_PLUS ? add2(a, b) : mul2(a, b), p0, p1);
+    return ADD == CUASR_OP_MINIMUM ? min3(acc, p0, p1) : max3(acc, p0, p1);
+  }
+
   // True when an out-of-range operand element may be replaced by NaN (float min/max rings: the NaN
   // product is ignored by min/max) — otherwise by zero, which must then be harmless: 0 (x) 0 has to be
   // the additive identity in effect (plus-times, or-and, xor-and, or-bitand).

@@ -268,6 +268,21 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         }
       };
       auto compute = [&](const T (&a)[8][EV], const T (&b)[8][EV]) {
+        if constexpr (kAK && kBK && RingT::kPackedPairs) {
+          // both fragments came from 16-byte loads along k: (k, k+1) are adjacent registers, so the pairs below
+          // are register renames, not moves
+#pragma unroll
+          for (int e = 0; e < EV; e += 2) {
+            uint64_t pa[8], pb[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { pa[i] = pack2(a[i][e], a[i][e + 1]); pb[i] = pack2(b[i][e], b[i][e + 1]); }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[i][j] = RingT::mac_packed(acc[i][j], pa[i], pb[j]);
+          }
+          return;
+        }
 #pragma unroll
         for (int e = 0; e < EV; e += 2)
 #pragma unroll
