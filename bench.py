@@ -236,7 +236,7 @@ def run_ours(args, wl):
     margs = Arguments((m, cols if world > 1 else n, k), (A, lda), (B, ldb), (C.data_ptr() + off, ldc),
                       (D.data_ptr() + off, ldc), (wl.alpha, wl.beta), wl.split_k_slices)
     ws = None
-    need = op.get_workspace_size(margs) or op.get_balance_workspace_size(margs)   # the second one is optional
+    need = op.get_workspace_size(margs) or op.get_optional_workspace_size(margs)   # the second one is optional
     if need:
         ws = torch.empty(need, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream()

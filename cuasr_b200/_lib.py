@@ -41,7 +41,7 @@ PROTOTYPES = {
     "cuasr_b200_srgemm_can_implement": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
-    "cuasr_b200_srgemm_balance_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
+    "cuasr_b200_srgemm_optional_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_push": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args), ctypes.c_int,
                                               ctypes.POINTER(ctypes.c_void_p)]),
     "cuasr_b200_srgemm_path": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args), ctypes.c_void_p,

@@ -107,7 +107,7 @@ class CudaBackend:
                               (dst.data_ptr() + off, n), (0.0, 0.0))
         stream = self.torch.cuda.current_stream(self.device)
         if self.workspace is None:
-            need = self.op.get_balance_workspace_size(args)
+            need = self.op.get_optional_workspace_size(args)
             self.workspace = self.torch.empty(max(need, 1), dtype=self.torch.uint8, device=self.device)
         st = self.op.initialize(args, self.workspace, stream)
         if st != self.Status.kSuccess:
@@ -210,7 +210,7 @@ class BlockedFloydWarshall:
         args = self.Arguments((m, n, k), (A, lda), (B, ldb), (C, ldc), (D, ldd), (0.0, 0.0))
         key = (m, n, k)
         if key not in self._workspaces:
-            need = self.op.get_balance_workspace_size(args)
+            need = self.op.get_optional_workspace_size(args)
             self._workspaces[key] = self.torch.empty(max(need, 1), dtype=self.torch.uint8, device=self.device)
         stream = self.torch.cuda.current_stream(self.device)
         st = self.op.initialize(args, self._workspaces[key], stream)

@@ -254,12 +254,27 @@ struct ExtraOutputs {
   void* ptr[kMaxDestinations - 1] = {};
 };
 
+// Re-packing of MN-contiguous fp32 operands into K-contiguous scratch, so that the kernel variant with packed
+// fp32x2 adds (both operands deliver (k, k+1) register pairs) can run.  Worth it only for the rings that variant
+// speeds up, and only for problems large enough for the TMA kernel.
+bool repack_pays(const cuasr_b200_desc_t& desc, const Normalised& p) {
+  const bool ring = (desc.add_op == CUASR_OP_MINIMUM || desc.add_op == CUASR_OP_MAXIMUM) &&
+                    (desc.mul_op == CUASR_OP_PLUS || desc.mul_op == CUASR_OP_MULTIPLIES);
+  return desc.dtype == CUASR_F32 && ring && static_cast<long long>(p.m) * p.n >= 256 * 256 && p.k >= 256 &&
+         (!p.a_kcontig || !p.b_kcontig);
+}
+size_t repack_operand_bytes(int rows, int k) { return align_up(static_cast<size_t>(rows) * align_up(k, 4) * 4, 256); }
+size_t repack_bytes(const cuasr_b200_desc_t& desc, const Normalised& p) {
+  if (!repack_pays(desc, p)) return 0;
+  return (p.a_kcontig ? 0 : repack_operand_bytes(p.m, p.k)) + (p.b_kcontig ? 0 : repack_operand_bytes(p.n, p.k));
+}
+
 template <typename T>
 int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int slices, const ExtraOutputs& extra) {
   DeviceState* dev = nullptr;
   if (!device_state(&dev)) return CUASR_STATUS_ERROR_INTERNAL;
   cudaStream_t stream = static_cast<cudaStream_t>(args.stream);
-  const Normalised p = normalise(desc, args);
+  Normalised p = normalise(desc, args);
 
   const T alpha = load_scalar<T>(args.alpha), beta = load_scalar<T>(args.beta);
   const T add_id = load_scalar<T>(args.add_identity), mul_id = load_scalar<T>(args.mul_identity);
@@ -281,6 +296,34 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
     constexpr int tk = kTileKBytes / sizeof(T);
     const BalancePlan wish = balance_plan(static_cast<long long>(tile_count(args)), dev->sms, (args.k + tk - 1) / tk);
     if (wish.pieces > 1 && args.workspace_bytes >= balance_workspace_bytes(desc, args, dev->sms)) plan = wish;
+  }
+  // the rest of an optional workspace holds K-contiguous copies of MN-contiguous fp32 operands
+  bool repacked = false;
+  if constexpr (std::is_same<T, float>::value) {
+    if (slices == 1 && args.workspace != nullptr) {
+      const size_t first = align_up(balance_workspace_bytes(desc, args, dev->sms), 256);
+      const size_t extra_bytes = repack_bytes(desc, p);
+      if (extra_bytes > 0 && args.workspace_bytes >= first + extra_bytes) {
+        char* cursor = static_cast<char*>(args.workspace) + first;
+        const long long ldt = static_cast<long long>(align_up(p.k, 4));
+        if (!p.a_kcontig) {
+          if (launch_transpose_f32(static_cast<const float*>(p.a), p.lda, p.m, p.k, reinterpret_cast<float*>(cursor),
+                                   ldt, stream) != cudaSuccess)
+            return CUASR_STATUS_ERROR_INTERNAL;
+          g_launches.fetch_add(1);
+          p.a = cursor; p.lda = ldt; p.a_kcontig = true;
+          cursor += repack_operand_bytes(p.m, p.k);
+        }
+        if (!p.b_kcontig) {
+          if (launch_transpose_f32(static_cast<const float*>(p.b), p.ldb, p.n, p.k, reinterpret_cast<float*>(cursor),
+                                   ldt, stream) != cudaSuccess)
+            return CUASR_STATUS_ERROR_INTERNAL;
+          g_launches.fetch_add(1);
+          p.b = cursor; p.ldb = ldt; p.b_kcontig = true;
+        }
+        repacked = true;
+      }
+    }
   }
   if (plan.pieces > 1) {
     const size_t ticket_bytes = ticket_bytes_for(args);
@@ -344,7 +387,8 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
       CUASR_FLOAT_RINGS(X)
       if constexpr (std::is_integral<T>::value) { CUASR_BIT_RINGS(X) }
 #undef X
-      if (launched) t_last_kernel = slices > 1 ? "tma_splitk" : plan.pieces > 1 ? "tma_balanced" : "tma";
+      if (launched)
+        t_last_kernel = slices > 1 ? "tma_splitk" : plan.pieces > 1 ? "tma_balanced" : repacked ? "tma_repacked" : "tma";
     }
   }
   if (!launched) {
@@ -443,12 +487,14 @@ size_t cuasr_b200_srgemm_workspace_size(const cuasr_b200_desc_t* desc, const cua
   return 0;
 }
 
-size_t cuasr_b200_srgemm_balance_workspace_size(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
+size_t cuasr_b200_srgemm_optional_workspace_size(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
   if (desc == nullptr || args == nullptr || validate(desc, args) != CUASR_STATUS_SUCCESS) return 0;
   if (args->split_k_slices > 1) return 0;
   DeviceState* dev = nullptr;
   if (!device_state(&dev)) return 0;
-  return balance_workspace_bytes(*desc, *args, dev->sms);
+  const size_t repack = repack_bytes(*desc, normalise(*desc, *args));
+  const size_t balance = balance_workspace_bytes(*desc, *args, dev->sms);
+  return repack > 0 ? align_up(balance, 256) + repack : balance;
 }
 
 int cuasr_b200_srgemm(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {

@@ -20,4 +20,10 @@ CUASR_ALL_TYPES(CUASR_OP_BINARY_OR, CUASR_OP_BINARY_AND)
 CUASR_INT_TYPES(CUASR_OP_BIT_XOR, CUASR_OP_BIT_AND)
 CUASR_INT_TYPES(CUASR_OP_BIT_OR, CUASR_OP_BIT_AND)
 CUASR_INT_TYPES(CUASR_OP_BIT_XOR, CUASR_OP_BINARY_AND)
+cudaError_t launch_transpose_f32(const float* src, long long ld_src, int rows, int K, float* dst, long long ld_dst,
+                                 cudaStream_t stream) {
+  dim3 grid((rows + 31) / 32, (K + 31) / 32);
+  transpose_to_kcontig_kernel<float><<<grid, 256, 0, stream>>>(src, ld_src, rows, K, dst, ld_dst);
+  return cudaGetLastError();
+}
 }  // namespace cuasr_b200

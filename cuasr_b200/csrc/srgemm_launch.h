@@ -42,4 +42,8 @@ cudaError_t launch_generic(const GenericParams<T>& params, int slices, cudaStrea
 template <int ADD, int MUL, typename T>
 cudaError_t launch_generic_reduce(const GenericParams<T>& params, int slices, cudaStream_t stream);
 
+// Copies an MN-contiguous rows x K operand into K-contiguous storage (see transpose_to_kcontig_kernel).
+cudaError_t launch_transpose_f32(const float* src, long long ld_src, int rows, int K, float* dst, long long ld_dst,
+                                 cudaStream_t stream);
+
 }  // namespace cuasr_b200

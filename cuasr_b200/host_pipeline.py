@@ -92,7 +92,7 @@ class HostSrgemm:
             self.s_run.wait_event(arrived)
             with torch.cuda.stream(self.s_run):
                 if self.workspace is None:
-                    need = self.op.get_balance_workspace_size(args)
+                    need = self.op.get_optional_workspace_size(args)
                     self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=self.device)
                 st = self.op.initialize(args, self.workspace, self.s_run)
                 if st == Status.kSuccess:

@@ -107,9 +107,10 @@ class _Operator:
     def get_workspace_size(self, args: Arguments) -> int:
         return int(self._fn("_workspace_size")(ctypes.byref(self._desc), ctypes.byref(self._pack(args))))
 
-    def get_balance_workspace_size(self, args: Arguments) -> int:
-        """Bytes of OPTIONAL workspace that let an unsplit launch balance its last wave over all SMs (0 = no gain)."""
-        return int(self._lib.cuasr_b200_srgemm_balance_workspace_size(ctypes.byref(self._desc),
+    def get_optional_workspace_size(self, args: Arguments) -> int:
+        """Bytes of OPTIONAL workspace for an unsplit launch (0 = nothing to gain): it buys a balanced last wave and,
+        for fp32 min/max-plus/times rings, K-contiguous copies of the operands so that packed adds can be used."""
+        return int(self._lib.cuasr_b200_srgemm_optional_workspace_size(ctypes.byref(self._desc),
                                                                       ctypes.byref(self._pack(args))))
 
     def initialize(self, args: Arguments, workspace=None, stream=None, workspace_bytes: int = 0) -> Status:

@@ -83,11 +83,15 @@ CUASR_B200_API size_t cuasr_b200_srgemm_workspace_size(const cuasr_b200_desc_t *
 CUASR_B200_API int cuasr_b200_srgemm(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 
 /* Optional.  The reference's unsplit Srgemm needs no workspace (device/srgemm.h:218-234 returns 0) and neither
- * does cuasr_b200_srgemm; but when the tile count is not a multiple of the SM count, the last wave leaves SMs
- * idle.  If the caller passes a workspace of at least this many bytes (0 = nothing to gain) to cuasr_b200_srgemm
- * or cuasr_b200_srgemm_push with split_k_slices == 1, the tiles of that last wave are cut along K, their pieces
- * fill the SMs, and the CTA that finishes a tile last folds the pieces in a fixed order.  Needs a current device. */
-CUASR_B200_API size_t cuasr_b200_srgemm_balance_workspace_size(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
+ * does cuasr_b200_srgemm.  A caller who passes a workspace of at least this many bytes (0 = nothing to gain) to
+ * cuasr_b200_srgemm or cuasr_b200_srgemm_push with split_k_slices == 1 gets two things, with identical results:
+ *  - load balance: when the tile count is not a multiple of the SM count, the tiles of the last wave are cut along
+ *    K, their pieces fill the SMs, and the CTA that finishes a tile last folds the pieces in a fixed order;
+ *  - fp32 min/max-plus and min/max-times rings: operands whose contiguous dimension is not K are first copied into
+ *    K-contiguous scratch (a bandwidth-bound pre-pass of well under 1 % of the run time), which lets the kernel use
+ *    packed fp32x2 adds for both products of a three-input min/max.
+ * Needs a current device. */
+CUASR_B200_API size_t cuasr_b200_srgemm_optional_workspace_size(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 
 /* cuasr_b200_srgemm whose epilogue also stores every element of D to `n_extra` (at most 7) further
  * matrices with the same layout and leading dimension as D.  The extra pointers may be peer-GPU memory that

@@ -199,7 +199,7 @@ def test_balanced_launch_with_optional_workspace(cuda_device, ring, dt):
             op = Srgemm(*RINGS[ring], dt, *layouts)
             args = Arguments((m, n, k), (dA, lda), (dB, ldb), (dC, ldc), (dD, ldc), (alpha, alpha))
             assert op.get_workspace_size(args) == 0
-            need = op.get_balance_workspace_size(args)
+            need = op.get_optional_workspace_size(args)
             assert need > 0, (m, n, k)
             ws = torch.empty(need, dtype=torch.uint8, device="cuda")
             for _ in range(2):   # twice: the tickets must be left clean
