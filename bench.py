@@ -135,6 +135,43 @@ def cpu_run(wl, lines: int, repeats: int = 1, warmup: int = 0):
     return 2.0 * mnk[0] * mnk[1] * mnk[2] / sec / 1e9, ("reference" if use_ref else "port"), cores, sec, D
 
 
+def reference_device_kernel(wl, A, lda, B, ldb, C, ldc, D, reps: int = 3):
+    """The reference's own SIMT kernel (default configuration, recompiled for sm_100a into oracle/_ref) on the
+    buffers the timed region used: its time, and whether its output has the bits of `D`.  None where that library
+    was not built or does not cover the workload (it is column-major only, without split-K)."""
+    import torch
+
+    import oracle
+    from cuasr_b200 import Layout, RINGS
+
+    if not oracle.have_ref_device() or wl.split_k_slices > 1 or any(l != Layout.COLUMN_MAJOR for l in wl.layouts):
+        return None
+    add_op, mul_op = RINGS[wl.ring]
+    out = torch.empty_like(D)
+    stream = torch.cuda.current_stream()
+
+    def run():
+        return oracle.ref_device_srgemm(add_op, mul_op, wl.dtype, (wl.m, wl.n, wl.k), A.data_ptr(), lda, B.data_ptr(),
+                                        ldb, C.data_ptr(), ldc, out.data_ptr(), ldc, wl.alpha, wl.beta,
+                                        stream.cuda_stream)
+
+    st = run()
+    if st != 0:
+        return None if st == -1 else {"error": f"status {st}"}
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(reps):
+        run()
+    t1.record(stream)
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / reps
+    return {"value": round(wl.ops / (ms * 1e-3) / 1e9, 2), "unit": "GOP/s", "ms": round(ms, 4), "launches": reps,
+            "bit_identical_to_ours": bool(torch.equal(out, D)),
+            "what": "the reference's cuasr::gemm::device::Srgemm, default configuration, recompiled for sm_100a, "
+                    "same device buffers"}
+
+
 def sample_lines(wl, target_gop: float = 9.0) -> int:
     """Lines of D whose product costs about `target_gop` GOP (a multiple of 32: the host SRGEMM works in
     32 x 32 blocks, tools/include/cuasr/reference/srgemm/host_srgemm.h:56-57)."""
@@ -349,6 +386,11 @@ def run_ours(args, wl):
             gops, kind, cores, sec, _ = cpu_run(wl, lines)
             cpu = {"value": round(gops, 3), "unit": "GOP/s", "cores": cores, "kind": kind,
                    "sample": f"first {lines} storage lines of D, one pass ({sec:.1f} s), all {cores} host threads"}
+        refdev = None
+        if world == 1 and not args.no_cpu_baseline:
+            assert op.initialize(margs, ws, stream) == Status.kSuccess and launch() == Status.kSuccess
+            torch.cuda.synchronize()
+            refdev = reference_device_kernel(wl, A, lda, B, ldb, C, ldc, D)
         peaks, peak_kind = measured_peaks()
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         peak_tops = sms * 128 * 2 * peaks["sm_max_mhz"] * 1e6 / 1e12
@@ -380,6 +422,7 @@ def run_ours(args, wl):
                          # summarised in profiles/bench_minplus_f32_8192_launch_list_and_dram.md
                          "traffic": 4552241664 if (wl.name == "minplus_f32_8192" and world == 1) else None},
             "cpu_baseline": cpu,
+            "reference_device_kernel": refdev,
             "parity_spot_check": parity,
         }
         print(json.dumps(line), flush=True)

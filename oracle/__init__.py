@@ -5,6 +5,10 @@ check and from the CPU-baseline leg of bench.py.
 `ref_srgemm(...)` -> oracle/_ref/libcuasr_ref.so, the reference's own host_srgemm.h compiled unmodified
                      (ref_host_srgemm.cpp); present only where it was built.
 Both take numpy arrays (any strides are NOT honoured: pass the buffer and its leading dimension).
+
+`ref_device_srgemm(...)` -> oracle/_ref/libcuasr_ref_device.so, the reference's own SIMT kernels recompiled for
+                     sm_100a (ref_device_srgemm.cu): device pointers in, column-major only, a few rings; used to
+                     time the reference as it stands on the same GPU and to compare bits.
 """
 from __future__ import annotations
 
@@ -16,6 +20,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_PATH = os.path.join(_HERE, "libcuasr_oracle.so")
 REF_PATH = os.path.join(_HERE, "_ref", "libcuasr_ref.so")
+REF_DEVICE_PATH = os.path.join(_HERE, "_ref", "libcuasr_ref_device.so")
 
 _ARGTYPES = [ctypes.c_int] * 9 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
                                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
@@ -35,6 +40,27 @@ def _load(path: str, symbol: str):
 
 def have_ref() -> bool:
     return os.path.exists(REF_PATH)
+
+
+def have_ref_device() -> bool:
+    return os.path.exists(REF_DEVICE_PATH)
+
+
+def ref_device_srgemm(add_op, mul_op, dtype, mnk, A, lda, B, ldb, C, ldc, D, ldd, alpha, beta, stream=0) -> int:
+    """Enqueue the reference's device SRGEMM (default configuration, column-major A, B, C, D) on `stream`.
+    A, B, C, D are device addresses.  Returns the reference's status (0 = success) or -1 when the (ring, element
+    type) pair is not among the ones built."""
+    if REF_DEVICE_PATH not in _libs:
+        lib = ctypes.CDLL(REF_DEVICE_PATH)
+        fn = lib.cuasr_refdev_srgemm
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_int] * 6 + [ctypes.c_void_p, ctypes.c_int] * 4 + [ctypes.c_void_p] * 3
+        _libs[REF_DEVICE_PATH] = (lib, fn)
+    _, fn = _libs[REF_DEVICE_PATH]
+    np_t = {0: np.float32, 1: np.float64, 2: np.int32, 3: np.uint32}[int(dtype)]
+    al, be = (np.array([v], dtype=np_t) for v in (alpha, beta))
+    return int(fn(int(add_op), int(mul_op), int(dtype), int(mnk[0]), int(mnk[1]), int(mnk[2]), int(A), int(lda),
+                  int(B), int(ldb), int(C), int(ldc), int(D), int(ldd), al.ctypes.data, be.ctypes.data, int(stream)))
 
 
 def max_threads(ref: bool = False) -> int:
