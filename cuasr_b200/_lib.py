@@ -36,7 +36,29 @@ class Args(ctypes.Structure):
     ]
 
 
-# name -> (restype, argtypes); every symbol include/cuasr_b200.h declares
+class ApspArgs(ctypes.Structure):          # cuasr_b200_apsp_args_t
+    _fields_ = [
+        ("dtype", ctypes.c_int32), ("algorithm", ctypes.c_int32), ("n", ctypes.c_int32), ("block", ctypes.c_int32),
+        ("iterations", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("D", ctypes.c_void_p), ("ldd", ctypes.c_int64),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+class ApspShardArgs(ctypes.Structure):     # cuasr_b200_apsp_shard_args_t
+    _fields_ = [
+        ("dtype", ctypes.c_int32), ("n", ctypes.c_int32), ("col0", ctypes.c_int32), ("cols", ctypes.c_int32),
+        ("D_cur", ctypes.c_void_p), ("ld_cur", ctypes.c_int64),
+        ("D_next", ctypes.c_void_p), ("ld_next", ctypes.c_int64),
+        ("n_peers", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("peer_next", ctypes.POINTER(ctypes.c_void_p)),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/*.h declares
 PROTOTYPES = {
     "cuasr_b200_srgemm_can_implement": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
@@ -50,6 +72,9 @@ PROTOTYPES = {
     "cuasr_b200_srgemm_splitk_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_splitk": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
     "cuasr_b200_srgemm_splitk_static": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
+    "cuasr_b200_apsp_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(ApspArgs)]),
+    "cuasr_b200_apsp": (ctypes.c_int, [ctypes.POINTER(ApspArgs)]),
+    "cuasr_b200_apsp_shard_squaring": (ctypes.c_int, [ctypes.POINTER(ApspShardArgs)]),
     "cuasr_b200_device_status": (ctypes.c_int, [ctypes.c_void_p]),
     "cuasr_b200_last_kernel": (ctypes.c_char_p, []),
     "cuasr_b200_launch_count": (ctypes.c_uint64, []),

@@ -22,7 +22,7 @@ from __future__ import annotations
 import math
 from typing import List, Optional, Sequence
 
-from .semiring import DType, Layout, Op, identity
+from .semiring import DType, Layout, Op, Status, identity
 
 
 class ShardedSquaring:
@@ -258,3 +258,64 @@ class BlockedFloydWarshall:
 
     def result_columns(self):
         return self.D
+
+
+# ---- the C entry points of include/cuasr_b200_apsp.h --------------------------------------------------------
+REPEATED_SQUARING, BLOCKED_FLOYD_WARSHALL = 0, 1
+
+
+def _apsp_args(dtype: DType, algorithm: int, n: int, D=0, ldd: Optional[int] = None, block: int = 0,
+               iterations: int = 0, workspace=0, workspace_bytes: int = 0, stream: int = 0):
+    from . import _lib
+
+    a = _lib.ApspArgs()
+    a.dtype, a.algorithm, a.n, a.block, a.iterations = int(dtype), int(algorithm), int(n), int(block), int(iterations)
+    a.D, a.ldd = int(D) or None, int(n if ldd is None else ldd)
+    a.workspace, a.workspace_bytes = int(workspace) or None, int(workspace_bytes)
+    a.stream = int(stream) or None
+    return a
+
+
+def device_solve_workspace_size(dtype: DType, algorithm: int, n: int, block: int = 0) -> int:
+    """cuasr_b200_apsp_workspace_size: bytes of device scratch `device_solve` needs."""
+    import ctypes
+
+    from . import _lib
+
+    return int(_lib.load().cuasr_b200_apsp_workspace_size(ctypes.byref(_apsp_args(dtype, algorithm, n, block=block))))
+
+
+def device_solve(D, n: int, dtype: DType = DType.F32, algorithm: int = BLOCKED_FLOYD_WARSHALL, ldd: Optional[int] = None,
+                 block: int = 0, iterations: int = 0, workspace=None, stream=None) -> Status:
+    """cuasr_b200_apsp: closes the n x n distance matrix `D` (a torch CUDA tensor or a device address) in place on
+    one GPU; enqueues on `stream` (default: the current torch stream) and returns.  `workspace`: a uint8 CUDA
+    tensor of at least `device_solve_workspace_size` bytes; allocated here when omitted."""
+    import ctypes
+
+    import torch
+
+    from . import _lib
+
+    if workspace is None:
+        workspace = torch.empty(max(1, device_solve_workspace_size(dtype, algorithm, n, block)), dtype=torch.uint8,
+                                device="cuda")
+    s = torch.cuda.current_stream().cuda_stream if stream is None else getattr(stream, "cuda_stream", stream)
+    ptr = D.data_ptr() if hasattr(D, "data_ptr") else int(D)
+    a = _apsp_args(dtype, algorithm, n, ptr, ldd, block, iterations, workspace.data_ptr(), workspace.numel(), s)
+    return Status(_lib.load().cuasr_b200_apsp(ctypes.byref(a)))
+
+
+def shard_squaring(dtype: DType, n: int, col0: int, cols: int, d_cur: int, ld_cur: int, d_next: int, ld_next: int,
+                   peer_next: Sequence[int] = (), workspace: int = 0, workspace_bytes: int = 0, stream: int = 0) -> Status:
+    """cuasr_b200_apsp_shard_squaring on device addresses: one rank's share of one squaring, pushed to the peers."""
+    import ctypes
+
+    from . import _lib
+
+    a = _lib.ApspShardArgs()
+    a.dtype, a.n, a.col0, a.cols = int(dtype), int(n), int(col0), int(cols)
+    a.D_cur, a.ld_cur, a.D_next, a.ld_next = int(d_cur) or None, int(ld_cur), int(d_next) or None, int(ld_next)
+    peers = (ctypes.c_void_p * max(1, len(peer_next)))(*[int(p) for p in peer_next])
+    a.n_peers, a.peer_next = len(peer_next), ctypes.cast(peers, ctypes.POINTER(ctypes.c_void_p))
+    a.workspace, a.workspace_bytes, a.stream = int(workspace) or None, int(workspace_bytes), int(stream) or None
+    return Status(_lib.load().cuasr_b200_apsp_shard_squaring(ctypes.byref(a)))

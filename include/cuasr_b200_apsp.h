@@ -1,0 +1,79 @@
+/*
+ * All-pairs shortest paths on top of the min-plus SRGEMM of cuasr_b200.h, as C entry points.
+ *
+ * The reference has no such layer: its README.md:338-342 names APSP as what the semiring GEMM and its
+ * epilogue (+) are for and leaves the driver to the user.  These calls are that driver: a sequence of
+ * cuasr_b200_srgemm launches on the caller's stream, nothing else.  Like the SRGEMM entry points they take
+ * DEVICE pointers owned by the caller, allocate nothing, never synchronise with the host and return
+ * cutlass::Status numbering (cuasr_status_t).
+ *
+ * Distances: n x n, element (i, j) = length of the best known path i -> j, stored at D[i + j * ldd].  The
+ * closure of a transposed matrix is the transpose of the closure, so a row-major matrix is passed as it is.
+ * Absent edges hold +infinity (or any value that stays larger than every path length under addition), the
+ * diagonal holds 0.
+ */
+#ifndef CUASR_B200_APSP_H
+#define CUASR_B200_APSP_H
+
+#include "cuasr_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum cuasr_apsp_algorithm {
+  /* D <- min(D, D (x) D), ceil(log2 n) times (or `iterations` times): 2 n^3 log2 n operations, every launch one
+   * large SRGEMM.  Shards over GPUs with one exchange per squaring (cuasr_b200_apsp_shard_squaring). */
+  CUASR_APSP_REPEATED_SQUARING = 0,
+  /* Three-phase blocked Floyd-Warshall: per block of `block` vertices close the diagonal block, update the
+   * column and the row panel through it, then D <- min(D, column panel (x) row panel).  2 n^3 operations. */
+  CUASR_APSP_BLOCKED_FLOYD_WARSHALL = 1
+} cuasr_apsp_algorithm_t;
+
+typedef struct cuasr_b200_apsp_args {
+  int32_t dtype;       /* CUASR_F32 or CUASR_F64 */
+  int32_t algorithm;   /* cuasr_apsp_algorithm_t */
+  int32_t n;           /* vertices */
+  int32_t block;       /* Floyd-Warshall block size, a multiple of 4; 0 = 1024 (the measured optimum at n = 16384) */
+  int32_t iterations;  /* repeated squaring: number of squarings; 0 = ceil(log2 n), enough for any graph */
+  int32_t reserved;
+  void *D;             /* distances, read and overwritten with the closure */
+  int64_t ldd;         /* >= n, in elements */
+  void *workspace;     /* at least cuasr_b200_apsp_workspace_size bytes, 256-byte aligned */
+  size_t workspace_bytes;
+  void *stream;        /* cudaStream_t */
+} cuasr_b200_apsp_args_t;
+
+/* Bytes of device scratch cuasr_b200_apsp needs: a second n x n matrix for repeated squaring; two panels and two
+ * diagonal blocks for Floyd-Warshall; plus, when a device is current, what the SRGEMM launches can use to balance
+ * their last wave (cuasr_b200_srgemm_optional_workspace_size).  0 for invalid arguments. */
+CUASR_B200_API size_t cuasr_b200_apsp_workspace_size(const cuasr_b200_apsp_args_t *args);
+
+/* Enqueues the whole solve on args->stream and returns.  CUASR_STATUS_ERROR_WORKSPACE_NULL when the workspace is
+ * missing or too small, CUASR_STATUS_ERROR_INVALID_PROBLEM for bad sizes or pointers. */
+CUASR_B200_API int cuasr_b200_apsp(const cuasr_b200_apsp_args_t *args);
+
+/* One squaring of a solve whose columns are sharded over GPUs: this rank owns columns [col0, col0 + cols) and
+ * computes  D_next[:, own] = min(D_cur[:, own], D_cur (x) D_cur[:, own])  from its full local copy D_cur, storing
+ * the block into its own D_next and, from the same epilogue, into the D_next of up to 7 peers (addresses this
+ * device can write: peer access or symmetric memory).  After every rank's launch and a barrier that orders them
+ * (for example a one-word NCCL all-reduce on the same streams) each D_next holds the complete next iterate and
+ * the roles of D_cur and D_next swap.  The workspace is optional (load balance only) and may be NULL. */
+typedef struct cuasr_b200_apsp_shard_args {
+  int32_t dtype;
+  int32_t n;
+  int32_t col0, cols;
+  const void *D_cur;  int64_t ld_cur;
+  void *D_next;       int64_t ld_next;   /* same leading dimension on every rank */
+  int32_t n_peers;    int32_t reserved;
+  void *const *peer_next;                /* n_peers base addresses of the other ranks' D_next */
+  void *workspace;    size_t workspace_bytes;
+  void *stream;
+} cuasr_b200_apsp_shard_args_t;
+
+CUASR_B200_API int cuasr_b200_apsp_shard_squaring(const cuasr_b200_apsp_shard_args_t *args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUASR_B200_APSP_H */

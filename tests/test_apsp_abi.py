@@ -1,0 +1,91 @@
+"""The C entry points of include/cuasr_b200_apsp.h: argument checks and sizes without a GPU, whole solves on one."""
+import numpy as np
+import pytest
+
+from cuasr_b200 import DType, Status, apsp
+
+
+def test_workspace_sizes_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("with a device the sizes also hold the optional SRGEMM scratch")
+    assert apsp.device_solve_workspace_size(DType.F32, apsp.REPEATED_SQUARING, 1024) == 4 * 1024 * 1024
+    assert apsp.device_solve_workspace_size(DType.F64, apsp.REPEATED_SQUARING, 1000) == 8 * 1000 * 1000
+    # Floyd-Warshall: column panel + row panel + two diagonal blocks
+    assert apsp.device_solve_workspace_size(DType.F32, apsp.BLOCKED_FLOYD_WARSHALL, 4096, 512) == 4 * (2 * 4096 * 512 + 2 * 512 * 512)
+    assert apsp.device_solve_workspace_size(DType.F32, apsp.BLOCKED_FLOYD_WARSHALL, 4096) == 4 * (2 * 4096 * 1024 + 2 * 1024 * 1024)
+    assert apsp.device_solve_workspace_size(DType.S32, apsp.REPEATED_SQUARING, 1024) == 0      # not a distance type
+    assert apsp.device_solve_workspace_size(DType.F32, 7, 1024) == 0
+    assert apsp.device_solve_workspace_size(DType.F32, apsp.BLOCKED_FLOYD_WARSHALL, 1024, 30) == 0   # block % 4
+
+
+def test_argument_checks_need_no_device():
+    import ctypes
+    from cuasr_b200 import _lib
+    lib = _lib.load()
+    call = lambda **kw: Status(lib.cuasr_b200_apsp(ctypes.byref(apsp._apsp_args(**kw))))
+    ok = dict(dtype=DType.F32, algorithm=apsp.REPEATED_SQUARING, n=64, D=4096, workspace=8192, workspace_bytes=1 << 20)
+    assert call(**dict(ok, D=0)) == Status.kErrorInvalidProblem
+    assert call(**dict(ok, n=0)) == Status.kErrorInvalidProblem
+    assert call(**dict(ok, ldd=63)) == Status.kErrorInvalidProblem
+    assert call(**dict(ok, D=4098)) == Status.kErrorMisalignedOperand
+    assert call(**dict(ok, workspace=0)) == Status.kErrorWorkspaceNull
+    assert call(**dict(ok, workspace_bytes=64 * 64 * 4 - 1)) == Status.kErrorWorkspaceNull
+    assert call(**dict(ok, workspace=8200)) == Status.kErrorMisalignedOperand
+    assert lib.cuasr_b200_apsp(None) == int(Status.kErrorInvalidProblem)
+    assert apsp.shard_squaring(DType.F32, 64, 32, 64, 4096, 64, 8192, 64) == Status.kErrorInvalidProblem   # columns past n
+    assert apsp.shard_squaring(DType.F32, 64, 0, 32, 0, 64, 8192, 64) == Status.kErrorInvalidProblem
+    assert apsp.shard_squaring(DType.F32, 64, 0, 32, 4096, 64, 8192, 64, peer_next=[1] * 8) == Status.kErrorInvalidProblem
+    assert lib.cuasr_b200_apsp_shard_squaring(None) == int(Status.kErrorInvalidProblem)
+
+
+def _graph(n, seed, dtype):
+    rng = np.random.default_rng(seed)
+    w = rng.integers(1, 101, size=(n, n)).astype(dtype)
+    w[rng.random((n, n)) >= 0.02] = np.inf
+    np.fill_diagonal(w, 0)
+    return w
+
+
+def _closure(w):
+    from scipy.sparse.csgraph import floyd_warshall
+    return floyd_warshall(np.where(np.isinf(w), 0, w).astype(np.float64), directed=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("algorithm", [apsp.REPEATED_SQUARING, apsp.BLOCKED_FLOYD_WARSHALL])
+@pytest.mark.parametrize("n,ld,block,dt", [(1024, 1024, 256, DType.F32), (1000, 1008, 256, DType.F32), (333, 333, 0, DType.F64),
+                                           (1537, 1540, 512, DType.F32)])
+def test_device_solve_equals_floyd_warshall_on_the_host(cuda_device, algorithm, n, ld, block, dt):
+    import torch
+    np_t = np.float32 if dt == DType.F32 else np.float64
+    w = _graph(n, n + block, np_t)
+    want = _closure(w)              # integer weights: exact in either element type, so equality is bit for bit
+    buf = np.full((n, ld), 7.0, dtype=np_t)          # column j of the matrix is row j of this array
+    buf[:, :n] = w.T
+    D = torch.from_numpy(buf).cuda()
+    assert apsp.device_solve(D, n, dt, algorithm, ldd=ld, block=block) == Status.kSuccess
+    torch.cuda.synchronize()
+    got = D.cpu().numpy()
+    assert np.array_equal(got[:, :n].T.astype(np.float64), want)
+    assert np.all(got[:, n:] == 7.0)                 # the padding of every column is untouched
+
+
+@pytest.mark.gpu
+def test_shard_squaring_pushes_to_every_destination(cuda_device):
+    """Two ranks emulated one after the other on one GPU: each computes its half of the columns and stores it into
+    both next-iterate matrices; together they must equal one unsharded squaring."""
+    import torch
+    n = 512
+    w = _graph(n, 5, np.float32)
+    cur = torch.from_numpy(np.ascontiguousarray(w.T)).cuda()
+    nxt = [torch.zeros_like(cur) for _ in range(2)]
+    s = torch.cuda.current_stream().cuda_stream
+    for rank in range(2):
+        st = apsp.shard_squaring(DType.F32, n, rank * 256, 256, cur.data_ptr(), n, nxt[rank].data_ptr(), n,
+                                 peer_next=[nxt[1 - rank].data_ptr()], stream=s)
+        assert st == Status.kSuccess
+    whole = cur.clone()
+    assert apsp.device_solve(whole, n, DType.F32, apsp.REPEATED_SQUARING, iterations=1) == Status.kSuccess
+    torch.cuda.synchronize()
+    assert torch.equal(nxt[0], whole) and torch.equal(nxt[1], whole)
