@@ -75,6 +75,10 @@ PROTOTYPES = {
     "cuasr_b200_apsp_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(ApspArgs)]),
     "cuasr_b200_apsp": (ctypes.c_int, [ctypes.POINTER(ApspArgs)]),
     "cuasr_b200_apsp_shard_squaring": (ctypes.c_int, [ctypes.POINTER(ApspShardArgs)]),
+    "cuasr_b200_flag_raise": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_uint32,
+                                             ctypes.c_void_p]),
+    "cuasr_b200_flag_wait": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
+                                            ctypes.c_void_p]),
     "cuasr_b200_device_status": (ctypes.c_int, [ctypes.c_void_p]),
     "cuasr_b200_last_kernel": (ctypes.c_char_p, []),
     "cuasr_b200_launch_count": (ctypes.c_uint64, []),

@@ -154,7 +154,8 @@ class BlockedFloydWarshall:
     SRGEMM (its epilogue (+) with C is what the reference's README.md:338-342 positions for exactly this): 2 n^3
     semiring operations in total instead of 2 n^3 log2(n) for repeated squaring.
 
-    D is column-major, n x n; rank g of G owns n / G consecutive columns and stores only those.  For every block
+    D is column-major, n x n; rank g of G owns n / G columns (every G-th block of `block` columns by default, see
+    `distribution`) and stores only those.  For every block
     K = [kb * b, (kb + 1) * b) of vertices:
       1. the rank that owns columns K closes the diagonal block (paths inside K) by ceil(log2 b) squarings of it;
       2. it updates the column panel  P_col = min(D[:, K], D[:, K] (x) D[K, K]*)  and every rank receives P_col
@@ -166,12 +167,19 @@ class BlockedFloydWarshall:
     floating-point weights the two orders of summation may round differently.
     """
 
-    def __init__(self, n: int, block: int, rank: int, world: int, device, mode: str = "push", group=None):
+    def __init__(self, n: int, block: int, rank: int, world: int, device, mode: str = "push", group=None,
+                 look_ahead: Optional[bool] = None, distribution: str = "cyclic"):
         import torch
         import torch.distributed as dist
 
         from .srgemm import Arguments, Srgemm, Status
 
+        self.look_ahead = world > 1 if look_ahead is None else bool(look_ahead)
+        if distribution not in ("cyclic", "contiguous"):
+            raise ValueError(distribution)
+        # "cyclic": rank g owns the column blocks g, g + G, g + 2G, ... so the extra work of the owner (closure and
+        # column panel) moves to another rank every step; "contiguous": one run of n / G columns per rank
+        self.distribution = distribution
         if n % world or (n // world) % block:
             raise ValueError(f"block size {block} must divide the {n // max(world, 1)} columns each rank owns")
         if mode not in ("push", "allgather"):
@@ -185,24 +193,45 @@ class BlockedFloydWarshall:
         self.D = torch.empty(n * self.cols, dtype=f32, device=device)          # my columns, ld = n
         self.p_row = torch.empty(block * self.cols, dtype=f32, device=device)  # ld = block
         self.diag = [torch.empty(block * block, dtype=f32, device=device) for _ in range(2)]
-        self.peer_pcol: List[List[int]] = [[], []]
+        self.peer_pcol: List[List[int]] = [[], [], []]
         if world > 1 and mode == "push":
             import torch.distributed._symmetric_memory as symm_mem
 
-            self.p_col = [symm_mem.empty(n * block, dtype=f32, device=device) for _ in range(2)]
+            self.p_col = [symm_mem.empty(n * block, dtype=f32, device=device) for _ in range(3)]
             handles = [symm_mem.rendezvous(t, dist.group.WORLD if group is None else group) for t in self.p_col]
             self._handles = handles
             self.peer_pcol = [[int(p) for p in h.buffer_ptrs] for h in handles]
+            # word 0: number of column panels delivered to me so far; words 1 + r: steps rank r has finished
+            self.sig = symm_mem.empty(64, dtype=torch.int32, device=device)
+            self._sig_handle = symm_mem.rendezvous(self.sig, dist.group.WORLD if group is None else group)
+            self.peer_sig = [int(p) for p in self._sig_handle.buffer_ptrs]
+            self.sig.zero_()
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)            # nobody raises a word that is about to be cleared
         else:
-            self.p_col = [torch.empty(n * block, dtype=f32, device=device) for _ in range(2)]
+            self.p_col = [torch.empty(n * block, dtype=f32, device=device) for _ in range(3)]
+        self.epoch = 0
+        self.wait_ms = 5000
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         col = Layout.COLUMN_MAJOR
         self.op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, col, col, col, add_identity=math.inf)
         self._workspaces = {}
         self.launches = 0
 
+    def owner(self, kb: int) -> int:
+        return kb % self.world if self.distribution == "cyclic" else (kb * self.b) // self.cols
+
+    def local_column(self, kb: int) -> int:
+        """First local column of block kb on the rank that owns it."""
+        return (kb // self.world) * self.b if self.distribution == "cyclic" else kb * self.b - self.c0
+
+    def owned_blocks(self) -> List[int]:
+        """Global indices of the column blocks this rank holds, in the order it stores them."""
+        return [kb for kb in range(self.n // self.b) if self.owner(kb) == self.rank]
+
     def load_columns(self, flat) -> None:
-        """`flat`: this rank's n x cols block of the weighted adjacency matrix (column-major, diagonal 0)."""
+        """`flat`: this rank's columns of the weighted adjacency matrix (column-major, n x cols, diagonal 0): the
+        column blocks `owned_blocks()` one after the other."""
         self.D.copy_(flat)
 
     def _srgemm(self, m, n, k, A, lda, B, ldb, C, ldc, D, ldd, extras=()):
@@ -220,41 +249,121 @@ class BlockedFloydWarshall:
             raise RuntimeError(f"SRGEMM failed: {st!r}")
         self.launches += 1
 
-    def solve(self) -> None:
+    def _closure_and_column_panel(self, kb: int) -> None:
+        """Run by the rank that owns block K = kb: phase 1 and the column panel of phase 2, delivered to every rank."""
         n, b, es = self.n, self.b, 4
-        torch = self.torch
+        k0 = kb * b
+        lc = self.local_column(kb)                              # first local column of block K
+        # phase 1: closure of the diagonal block by repeated squaring of a private copy
+        self.diag[0].view(b, b).copy_(self.D.view(self.cols, n)[lc:lc + b, k0:k0 + b])
+        cur = 0
+        for _ in range(max(1, math.ceil(math.log2(b)))):
+            s, d = self.diag[cur].data_ptr(), self.diag[1 - cur].data_ptr()
+            self._srgemm(b, b, b, s, b, s, b, s, b, d, b)
+            cur = 1 - cur
+        star = self.diag[cur].data_ptr()
+        # phase 2, column panel: P_col = min(D[:, K], D[:, K] (x) D[K, K]*)
+        panel = self.D.data_ptr() + lc * n * es
+        extras = [p for r, p in enumerate(self.peer_pcol[kb % 3]) if r != self.rank]
+        self._srgemm(n, b, b, panel, n, star, b, panel, n, self.p_col[kb % 3].data_ptr(), n, extras)
+
+    def _phase3(self, pcp: int, lo: int, hi: int) -> None:
+        """D[:, lo:hi] = min(D[:, lo:hi], P_col (x) P_row[:, lo:hi]) over my local columns lo..hi, in place (C aliases
+        D; the operands are copies)."""
+        if hi <= lo:
+            return
+        n, b, es = self.n, self.b, 4
+        d = self.D.data_ptr() + lo * n * es
+        self._srgemm(n, hi - lo, b, pcp, n, self.p_row.data_ptr() + lo * b * es, b, d, n, d, n)
+
+    # -- ordering between ranks ------------------------------------------------------------------------------
+    # "allgather" mode: one NCCL broadcast per panel.  "push" mode: the owner's SRGEMM epilogue has already stored the
+    # panel into every rank's buffer; what remains is ordering, and that is one-sided (cuasr_b200_flag_raise / _wait):
+    # the owner raises "panels delivered" on every rank and goes on, a consumer waits for its own copy of that word.
+    # A collective here would make the owner wait until the slowest consumer arrives, i.e. run in lockstep with it.
+    def _raise(self, word: int, value: int) -> None:
+        import ctypes
+
+        from . import _lib
+
+        ptrs = (ctypes.c_void_p * self.world)(*[p + 4 * word for p in self.peer_sig])
+        stream = self.torch.cuda.current_stream(self.device).cuda_stream
+        st = _lib.load().cuasr_b200_flag_raise(ptrs, self.world, value, stream)
+        if st != 0:
+            raise RuntimeError(f"flag raise failed: {Status(st)!r}")
+        self.launches += 1
+
+    def _wait(self, word: int, count: int, value: int) -> None:
+        from . import _lib
+
+        stream = self.torch.cuda.current_stream(self.device).cuda_stream
+        st = _lib.load().cuasr_b200_flag_wait(self.sig.data_ptr() + 4 * word, count, value, self.wait_ms, stream)
+        if st != 0:
+            raise RuntimeError(f"flag wait failed: {Status(st)!r}")
+        self.launches += 1
+
+    def _send_panel(self, kb: int, base: int) -> None:
+        """Run by the owner of block kb.  The panel goes into buffer kb % 3, which every rank last read in step
+        kb - 3: wait until all of them have reported that step finished, then compute, push and announce."""
+        flags = self.world > 1 and self.mode == "push"
+        if flags and kb >= 3:
+            self._wait(1, self.world, base + kb - 2)
+        self._closure_and_column_panel(kb)
+        if flags:
+            self._raise(0, base + kb + 1)
+
+    def _receive_panel(self, kb: int, base: int) -> None:
+        """Every rank, once per block and in block order: afterwards P_col of block kb is complete in buffer kb % 3."""
+        if self.world == 1:
+            return
+        owner = self.owner(kb)
+        if self.mode == "push":
+            if owner != self.rank:
+                self._wait(0, 1, base + kb + 1)
+        else:
+            self.dist.broadcast(self.p_col[kb % 3], src=owner, group=self.group)
+
+    def solve(self) -> None:
+        """With look-ahead (the default with more than one rank) the owner of the NEXT block works ahead: it updates
+        that block's columns first, closes the block and sends its column panel before it finishes phase 3 of the
+        current block.  The chain panel -> next panel is then (row-panel piece, one block of phase 3, closure, column
+        panel) instead of a whole step, and the ranks that only consume never wait.  Three panel buffers plus the
+        "step finished" words keep a fast owner from overwriting a panel a slow rank still reads."""
+        n, b, es = self.n, self.b, 4
         Dp = self.D.data_ptr()
-        squarings = max(1, math.ceil(math.log2(b)))
-        for kb in range(n // b):
+        blocks = n // b
+        ahead = self.look_ahead
+        base = self.epoch * (blocks + 4)          # flag values of this solve start above those of the last one
+        self.epoch += 1
+        if self.world > 1:
+            # a rank may still be reading the panels of a previous solve: nobody sends before everybody is here
+            self.dist.all_reduce(self._flag, group=self.group)
+        if self.rank == 0:
+            self._send_panel(0, base)
+        for kb in range(blocks):
             k0 = kb * b
-            owner = k0 // self.cols
-            pc = self.p_col[kb % 2]
-            pcp = pc.data_ptr()
-            if self.rank == owner:
-                lc = k0 - self.c0                                   # first local column of block K
-                # phase 1: closure of the diagonal block by repeated squaring of a private copy
-                src = self.D.view(self.cols, n)[lc:lc + b, k0:k0 + b]
-                self.diag[0].view(b, b).copy_(src)
-                cur = 0
-                for _ in range(squarings):
-                    s, d = self.diag[cur].data_ptr(), self.diag[1 - cur].data_ptr()
-                    self._srgemm(b, b, b, s, b, s, b, s, b, d, b)
-                    cur = 1 - cur
-                star = self.diag[cur].data_ptr()
-                # phase 2, column panel: P_col = min(D[:, K], D[:, K] (x) D[K, K]*), delivered to every rank
-                panel = Dp + lc * n * es
-                extras = [p for r, p in enumerate(self.peer_pcol[kb % 2]) if r != self.rank]
-                self._srgemm(n, b, b, panel, n, star, b, panel, n, pcp, n, extras)
-            if self.world > 1:
-                if self.mode == "push":
-                    self.dist.all_reduce(self._flag, group=self.group)      # stream-ordered barrier
-                else:
-                    self.dist.broadcast(pc, src=owner, group=self.group)
+            pcp = self.p_col[kb % 3].data_ptr()
+            if not (ahead and self.mode != "push" and kb > 0 and self.owner(kb) == self.rank):
+                self._receive_panel(kb, base)     # (a broadcasting owner that worked ahead has already joined it)
             # phase 2, my piece of the row panel: P_row = min(D[K, mine], D[K, K]* (x) D[K, mine]); D[K, K]* = P_col[K, :]
             rows = Dp + k0 * es
             self._srgemm(b, self.cols, b, pcp + k0 * es, n, rows, n, rows, n, self.p_row.data_ptr(), b)
-            # phase 3: D[:, mine] = min(D[:, mine], P_col (x) P_row), in place (C aliases D; the operands are copies)
-            self._srgemm(n, self.cols, b, pcp, n, self.p_row.data_ptr(), b, Dp, n, Dp, n)
+            nxt = kb + 1
+            mine_next = nxt < blocks and self.owner(nxt) == self.rank
+            if ahead and mine_next:
+                lc = self.local_column(nxt)
+                self._phase3(pcp, lc, lc + b)
+                self._send_panel(nxt, base)
+                if self.mode != "push":
+                    self._receive_panel(nxt, base)          # the root's side of the broadcast, early
+                self._phase3(pcp, 0, lc)
+                self._phase3(pcp, lc + b, self.cols)
+            else:
+                self._phase3(pcp, 0, self.cols)
+                if mine_next:
+                    self._send_panel(nxt, base)
+            if self.world > 1 and self.mode == "push":
+                self._raise(1 + self.rank, base + kb + 1)   # step kb finished here: its panel buffer may be reused
 
     def result_columns(self):
         return self.D

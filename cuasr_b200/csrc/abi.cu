@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/cuasr_b200.h"
+#include "../../include/cuasr_b200_apsp.h"
 #include "srgemm_launch.h"
 #include "srgemm_path.cuh"
 
@@ -286,12 +287,16 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
   unsigned int* tickets = nullptr;
   T* partial = nullptr;
   BalancePlan plan{static_cast<int>(tile_count(args)), 1};
+  // partials are moved 16 bytes at a time and re-packed operands are read by TMA: a workspace that does not start
+  // on a 16-byte boundary is an error where it is required and is left unused where it is optional
+  const bool workspace_aligned = reinterpret_cast<uintptr_t>(args.workspace) % 16 == 0;
   if (slices > 1) {
     const size_t need = splitk_workspace_bytes(desc, args);
     if (args.workspace == nullptr) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
     if (args.workspace_bytes < need) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+    if (!workspace_aligned) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
     plan = BalancePlan{0, slices};
-  } else if (args.workspace != nullptr) {
+  } else if (args.workspace != nullptr && workspace_aligned) {
     // an optional workspace on an unsplit launch buys load balancing, if it is large enough for the plan
     constexpr int tk = kTileKBytes / sizeof(T);
     const BalancePlan wish = balance_plan(static_cast<long long>(tile_count(args)), dev->sms, (args.k + tk - 1) / tk);
@@ -300,7 +305,7 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
   // the rest of an optional workspace holds K-contiguous copies of MN-contiguous fp32 operands
   bool repacked = false;
   if constexpr (std::is_same<T, float>::value) {
-    if (slices == 1 && args.workspace != nullptr) {
+    if (slices == 1 && args.workspace != nullptr && workspace_aligned) {
       const size_t first = align_up(balance_workspace_bytes(desc, args, dev->sms), 256);
       const size_t extra_bytes = repack_bytes(desc, p);
       if (extra_bytes > 0 && args.workspace_bytes >= first + extra_bytes) {
@@ -440,6 +445,46 @@ int run(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args, int slices
     case CUASR_U32: return run_typed<uint32_t>(*desc, *args, slices, extra);
     default: return CUASR_STATUS_ERROR_INVALID_DATA_TYPE;
   }
+}
+
+// ---- one-sided flags between GPUs --------------------------------------------------------------------------
+// A producer raises a word in every consumer's memory after the kernel whose peer stores it announces; a consumer
+// waits for its own copy of the word on its own stream.  Neither side ever waits for the other to ARRIVE at a
+// collective, which is what lets the owner of a panel run ahead of the ranks that only consume it.
+constexpr int kMaxFlagTargets = 8;
+constexpr int kMaxFlagWords = 64;
+struct FlagTargets {
+  unsigned int* ptr[kMaxFlagTargets];
+};
+
+// Stream order puts this kernel after the stores it announces; the fence makes them visible system-wide first.
+// atomicMax keeps the word monotonic when several producers raise it in turn.
+__global__ void flag_raise_kernel(FlagTargets targets, int count, unsigned int value) {
+  const int i = threadIdx.x;
+  if (i < count) {
+    __threadfence_system();
+    atomicMax_system(targets.ptr[i], value);
+  }
+}
+
+// Thread i waits until word i is at least `value`.  The wait is bounded twice (wall time and iterations); when it
+// runs out the kernel records kDeviceTimeoutPeerFlag in the status word and returns, so the stream keeps moving and
+// the host finds the code with cuasr_b200_device_status.
+__global__ void flag_wait_kernel(const unsigned int* words, int count, unsigned int value, unsigned long long limit_ns,
+                                 unsigned int* status) {
+  const int i = threadIdx.x;
+  if (i >= count) return;
+  unsigned long long start, now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+  for (unsigned int spin = 0; spin < (1u << 26); ++spin) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(words + i) : "memory");
+    if (v >= value) return;
+    __nanosleep(256);
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - start > limit_ns) break;
+  }
+  report_device_error(status, kDeviceTimeoutPeerFlag);
 }
 
 // ---- built-in scratch for cuasr_b200_srgemm_splitk_static --------------------------------------------
@@ -600,6 +645,33 @@ int cuasr_b200_device_status(void* stream) {
   if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
   if (host != 0) cudaMemsetAsync(dev->status, 0, sizeof(unsigned int), s);
   return static_cast<int>(host);
+}
+
+int cuasr_b200_flag_raise(void* const* words, int count, uint32_t value, void* stream) {
+  if (words == nullptr || count < 1 || count > kMaxFlagTargets) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  FlagTargets targets = {};
+  for (int i = 0; i < count; ++i) {
+    if (words[i] == nullptr) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+    if (reinterpret_cast<uintptr_t>(words[i]) % 4 != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+    targets.ptr[i] = static_cast<unsigned int*>(words[i]);
+  }
+  flag_raise_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(targets, count, value);
+  if (cudaGetLastError() != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+  g_launches.fetch_add(1);
+  return CUASR_STATUS_SUCCESS;
+}
+
+int cuasr_b200_flag_wait(const void* words, int count, uint32_t value, uint32_t timeout_ms, void* stream) {
+  if (words == nullptr || count < 1 || count > kMaxFlagWords || timeout_ms == 0 || timeout_ms > 10000)
+    return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (reinterpret_cast<uintptr_t>(words) % 4 != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+  DeviceState* dev = nullptr;
+  if (!device_state(&dev)) return CUASR_STATUS_ERROR_INTERNAL;
+  flag_wait_kernel<<<1, kMaxFlagWords, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned int*>(words), count, value, 1000000ull * timeout_ms, dev->status);
+  if (cudaGetLastError() != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+  g_launches.fetch_add(1);
+  return CUASR_STATUS_SUCCESS;
 }
 
 const char* cuasr_b200_last_kernel(void) { return t_last_kernel; }

@@ -66,7 +66,8 @@ typedef struct cuasr_b200_args {
                                        accumulator (kernel/srgemm.h:220-221) */
   cuasr_b200_scalar_t mul_identity; /* MultiplicationOp::Identity: used only to decide whether C is read
                                        (semiring_linear_combination.h:118-125) */
-  void *workspace;                  /* device scratch of at least cuasr_b200_*_workspace_size bytes, or NULL */
+  void *workspace;                  /* device scratch of at least cuasr_b200_*_workspace_size bytes, 16-byte
+                                       aligned (any cudaMalloc result is), or NULL */
   size_t workspace_bytes;
   void *stream;                     /* cudaStream_t */
 } cuasr_b200_args_t;

@@ -73,6 +73,22 @@ typedef struct cuasr_b200_apsp_shard_args {
 
 CUASR_B200_API int cuasr_b200_apsp_shard_squaring(const cuasr_b200_apsp_shard_args_t *args);
 
+/* One-sided ordering between GPUs, for solves in which one rank produces what the others consume (the column
+ * panels of the sharded Floyd-Warshall solve).  A barrier makes the producer wait for the slowest consumer to
+ * arrive; with these two calls the producer only announces, and each consumer waits for the announcement alone.
+ *
+ * cuasr_b200_flag_raise: after everything already enqueued on `stream` (in particular a cuasr_b200_srgemm_push
+ * whose peer stores it announces), raise each of `count` (at most 8) 32-bit words to at least `value`.  The
+ * words are device addresses this GPU can write: its own memory or peers'.  Values only grow.
+ *
+ * cuasr_b200_flag_wait: hold `stream` until each of `count` (at most 64) consecutive words of THIS GPU's memory
+ * is at least `value`.  The wait gives up after `timeout_ms` (1..10000): the kernel then records code 3 in the
+ * device status word (cuasr_b200_device_status) and lets the stream continue.  The word must be raised by another
+ * GPU or by an earlier operation of the same stream; never wait on one stream of a GPU for a kernel that has to
+ * run on another stream of the same GPU. */
+CUASR_B200_API int cuasr_b200_flag_raise(void *const *words, int count, uint32_t value, void *stream);
+CUASR_B200_API int cuasr_b200_flag_wait(const void *words, int count, uint32_t value, uint32_t timeout_ms, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -89,3 +89,26 @@ def test_shard_squaring_pushes_to_every_destination(cuda_device):
     assert apsp.device_solve(whole, n, DType.F32, apsp.REPEATED_SQUARING, iterations=1) == Status.kSuccess
     torch.cuda.synchronize()
     assert torch.equal(nxt[0], whole) and torch.equal(nxt[1], whole)
+
+
+@pytest.mark.gpu
+def test_flags_raise_wait_and_a_wait_that_runs_out(cuda_device):
+    """The one-sided flags of the sharded Floyd-Warshall solve, on one stream of one GPU: a raised word lets the wait
+    through, values only grow, and a wait nothing answers ends by itself with status 3 instead of hanging."""
+    import ctypes
+    import torch
+    from cuasr_b200 import _lib, device_status
+    lib = _lib.load()
+    words = torch.zeros(8, dtype=torch.int32, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    ptrs = (ctypes.c_void_p * 3)(*[words.data_ptr() + 4 * i for i in range(3)])
+    assert lib.cuasr_b200_flag_raise(ptrs, 3, 5, s) == 0
+    assert lib.cuasr_b200_flag_wait(words.data_ptr(), 3, 5, 100, s) == 0
+    assert lib.cuasr_b200_flag_raise(ptrs, 3, 3, s) == 0                     # lower than what is there: no effect
+    assert device_status() == 0
+    assert words.tolist() == [5, 5, 5, 0, 0, 0, 0, 0]
+    assert lib.cuasr_b200_flag_wait(words.data_ptr() + 12, 1, 1, 50, s) == 0   # word 3 stays 0: runs out after 50 ms
+    assert device_status() == 3
+    assert device_status() == 0                                              # reading the status clears it
+    assert lib.cuasr_b200_flag_wait(words.data_ptr(), 1, 1, 0, s) == int(Status.kErrorInvalidProblem)
+    assert lib.cuasr_b200_flag_raise(ptrs, 9, 1, s) == int(Status.kErrorInvalidProblem)

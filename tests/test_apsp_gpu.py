@@ -76,15 +76,16 @@ def test_blocked_floyd_warshall_equals_repeated_squaring(cuda_device):
     n, seed = 1024, 13
     flat = random_graph(n, 0.01, seed, cuda_device)
     want = cpu_apsp(flat.cpu().numpy(), n, ShardedSquaring.squarings_needed(n))
-    for block in (256, 512, 1024):
-        solver = BlockedFloydWarshall(n, block, 0, 1, cuda_device)
+    for block, look_ahead in ((256, False), (512, False), (1024, False), (128, True), (256, True), (1024, True)):
+        # look_ahead reorders the launches the way the multi-rank solve does (next block's columns first)
+        solver = BlockedFloydWarshall(n, block, 0, 1, cuda_device, look_ahead=look_ahead)
         solver.load_columns(flat)
         solver.solve()
         torch.cuda.synchronize()
-        assert np.array_equal(solver.result_columns().cpu().numpy(), want), f"block {block}"
+        assert np.array_equal(solver.result_columns().cpu().numpy(), want), f"block {block} look_ahead {look_ahead}"
 
 
-def _fw_rank(rank, world, port, n, seed, mode, out):
+def _fw_rank(rank, world, port, n, seed, mode, distribution, out):
     import torch
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -92,17 +93,22 @@ def _fw_rank(rank, world, port, n, seed, mode, out):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     cols = n // world
-    solver = BlockedFloydWarshall(n, 128, rank, world, dev, mode=mode)
-    solver.load_columns(random_graph(n, 0.01, seed, dev, rows=(rank * cols, cols)))
+    solver = BlockedFloydWarshall(n, 128, rank, world, dev, mode=mode, distribution=distribution)
+    solver.load_columns(torch.cat([random_graph(n, 0.01, seed, dev, rows=(kb * 128, 128)) for kb in solver.owned_blocks()]))
+    out[("blocks", mode, rank)] = solver.owned_blocks()
     solver.solve()
+    solver.solve()          # a second solve of the closed matrix changes nothing and reuses the panel buffers
     torch.cuda.synchronize()
+    from cuasr_b200 import device_status
+    out[("status", mode, rank)] = device_status()     # 3 would mean a wait for a peer's flag ran out
     out[(mode, rank)] = solver.result_columns().cpu().numpy()
     dist.barrier()
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("distribution", ["cyclic", "contiguous"])
 @pytest.mark.parametrize("mode", ["allgather", "push"])
-def test_multi_gpu_blocked_floyd_warshall(mode):
+def test_multi_gpu_blocked_floyd_warshall(mode, distribution):
     import torch
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 4)
@@ -113,11 +119,12 @@ def test_multi_gpu_blocked_floyd_warshall(mode):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     out = mp.Manager().dict()
-    mp.spawn(_fw_rank, args=(world, port, n, seed, mode, out), nprocs=world, join=True)
+    mp.spawn(_fw_rank, args=(world, port, n, seed, mode, distribution, out), nprocs=world, join=True)
     want = cpu_apsp(random_graph(n, 0.01, seed, "cpu").numpy(), n, ShardedSquaring.squarings_needed(n))
-    cols = n // world
     for rank in range(world):
-        assert np.array_equal(out[(mode, rank)], want[rank * cols * n:(rank + 1) * cols * n]), f"{mode}: rank {rank}"
+        assert out[("status", mode, rank)] == 0
+        mine = np.concatenate([want[kb * 128 * n:(kb + 1) * 128 * n] for kb in out[("blocks", mode, rank)]])
+        assert np.array_equal(out[(mode, rank)], mine), f"{mode} {distribution}: rank {rank}"
 
 
 def _rank(rank, world, port, n, seed, mode, out):

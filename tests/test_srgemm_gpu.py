@@ -280,6 +280,14 @@ def test_status_codes(cuda_device):
     par = SrgemmSplitKParallel(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL)
     assert par.get_workspace_size(bad) >= 4 * 64 * 64 * 2
     assert par(bad, None) == Status.kErrorWorkspaceNull
+    # a required workspace that does not start on a 16-byte boundary is refused, an optional one is left unused
+    ws = torch.zeros(par.get_workspace_size(bad) + 64, dtype=torch.uint8, device="cuda")
+    assert par(bad, ws.data_ptr() + 4, workspace_bytes=ws.numel() - 4) == Status.kErrorMisalignedOperand
+    big = Arguments((640, 640, 4096), (torch.zeros(640 * 4096, device="cuda"), 640), (torch.zeros(4096 * 640, device="cuda"), 4096),
+                    (None, 640), (torch.zeros(640 * 640, device="cuda"), 640))
+    ows = torch.zeros(op.get_optional_workspace_size(big) + 64, dtype=torch.uint8, device="cuda")
+    assert op(big, ows.data_ptr() + 4, workspace_bytes=ows.numel() - 4) == Status.kSuccess and op.last_kernel() == "tma"
+    assert op(big, ows) == Status.kSuccess and op.last_kernel() != "tma"
     # empty problem, short leading dimension, misaligned pointer, unsupported ring
     assert op.can_implement(Arguments((0, 64, 64), (x, 64), (x, 64), (x, 64), (x, 64))) == Status.kErrorInvalidProblem
     assert op.can_implement(Arguments((64, 64, 64), (x, 32), (x, 64), (x, 64), (x, 64))) == Status.kErrorInvalidProblem
