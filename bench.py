@@ -420,7 +420,7 @@ def run_ours(args, wl):
                          "hbm_peak_gbs": peaks["hbm_gbs"],
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
                          # summarised in profiles/bench_minplus_f32_8192_launch_list_and_dram.md
-                         "traffic": 4552241664 if (wl.name == "minplus_f32_8192" and world == 1) else None},
+                         "traffic": 3757164032 if (wl.name == "minplus_f32_8192" and world == 1) else None},
             "cpu_baseline": cpu,
             "reference_device_kernel": refdev,
             "parity_spot_check": parity,
