@@ -82,6 +82,16 @@ struct Ring {
       return min3(acc, mul(a0, b0), mul(a1, b1));
     } else if constexpr (std::is_same<T, float>::value && ADD == CUASR_OP_MAXIMUM) {
       return max3(acc, mul(a0, b0), mul(a1, b1));
+    } else if constexpr (std::is_same<T, int32_t>::value && MUL == CUASR_OP_PLUS && ADD == CUASR_OP_MINIMUM) {
+      // 32-bit integer tropical rings: one fused add-then-min/max instruction per product (the DPX family of
+      // sm_90 and later); the sum wraps like the reference's plain `a + b`
+      return __viaddmin_s32(a1, b1, __viaddmin_s32(a0, b0, acc));
+    } else if constexpr (std::is_same<T, int32_t>::value && MUL == CUASR_OP_PLUS && ADD == CUASR_OP_MAXIMUM) {
+      return __viaddmax_s32(a1, b1, __viaddmax_s32(a0, b0, acc));
+    } else if constexpr (std::is_same<T, uint32_t>::value && MUL == CUASR_OP_PLUS && ADD == CUASR_OP_MINIMUM) {
+      return __viaddmin_u32(a1, b1, __viaddmin_u32(a0, b0, acc));
+    } else if constexpr (std::is_same<T, uint32_t>::value && MUL == CUASR_OP_PLUS && ADD == CUASR_OP_MAXIMUM) {
+      return __viaddmax_u32(a1, b1, __viaddmax_u32(a0, b0, acc));
     } else {
       return add(mul(a1, b1), add(mul(a0, b0), acc));
     }

@@ -30,7 +30,7 @@ constexpr bool tma_instantiated() {
                         !(ADD == CUASR_OP_BIT_OR && MUL == CUASR_OP_BINARY_AND);
   if (std::is_same<T, float>::value) return tropical || minmax || times;
   if (std::is_same<T, double>::value) return tropical || minmax || times;
-  return bits;  // int32_t, uint32_t
+  return bits || tropical || minmax;  // int32_t, uint32_t
 }
 
 // Launches srgemm_generic_kernel<Ring<ADD, MUL, T>> on a (ceil(N/64), ceil(M/64), slices) grid.

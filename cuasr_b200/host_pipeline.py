@@ -8,13 +8,23 @@ lines of the other operand and of C go in on one stream, the SRGEMM of that chun
 its inputs have arrived, and the finished chunk of D goes out on a third, so host-to-device copies, math and
 device-to-host copies of different chunks run at the same time.  The arithmetic is the same SRGEMM, chunk by chunk,
 so the result is bit-identical to the one-shot call.
+
+The first chunk would otherwise wait for the whole shared operand.  Where that operand's K range is a run of whole
+storage lines (column-major A, or row-major B for a row-major D) it is sent in a few K pieces instead, and the first
+chunk is computed piece by piece, `D <- (alpha (x) A_p (x)(+) B_p) (+) D`, each piece as soon as it has arrived;
+(x) distributes over (+), and every ring except floating-point plus-times is exact, so the bits do not change
+(plus-times on floats keeps the one-piece schedule).
 """
 from __future__ import annotations
 
 from typing import Optional
 
-from .semiring import DType, Layout, Status
+from .semiring import DType, Layout, Op, Status
 from .srgemm import Arguments, Srgemm
+
+
+def _address(ref) -> int:
+    return ref.data_ptr() if hasattr(ref, "data_ptr") else int(ref)
 
 
 class HostSrgemm:
@@ -49,6 +59,10 @@ class HostSrgemm:
         self.extra = extra_outputs_per_chunk       # optional: callable(chunk_index, byte_offset) -> list of peer pointers
         self.workspace = None
         self.launches = 0
+        # K pieces of the shared operand for the first chunk (see the module docstring)
+        shared_lines_are_k = (col_c and la == Layout.COLUMN_MAJOR) or (not col_c and lb == Layout.ROW_MAJOR)
+        exact = not (operator.add_op == Op.PLUS and operator.dtype in (DType.F32, DType.F64))
+        self.k_pieces = 4 if (self.chunkable and shared_lines_are_k and exact and k % 4 == 0 and k >= 512) else 1
 
     def _chunk_args(self, j: int):
         """Arguments of chunk j and the element ranges of B (or A), C and D it touches."""
@@ -69,6 +83,41 @@ class HostSrgemm:
                              (self.dD.data_ptr() + out.start * self.es, self.ldc), (self.alpha, self.beta))
         return args, moving, out
 
+    def _launch(self, args, extras, what: str) -> None:
+        torch = self.torch
+        with torch.cuda.stream(self.s_run):
+            st = self.op.initialize(args, self.workspace, self.s_run)
+            if st == Status.kSuccess:
+                st = self.op.run_push(extras, self.s_run) if extras else self.op.run(self.s_run)
+            if st != Status.kSuccess:
+                raise RuntimeError(f"SRGEMM failed on {what}: {st!r}")
+            self.launches += 1
+
+    def _first_chunk_by_k_pieces(self, args, shared_dev, shared_host, extras) -> None:
+        """Chunk 0 as k_pieces accumulating launches, piece p as soon as K piece p of the shared operand is there."""
+        torch = self.torch
+        kp = self.k // self.k_pieces
+        line = self.m if self.col_c else self.n            # elements per K line of the shared operand
+        (m, n, _), es = args.problem_size, self.es
+        for p in range(self.k_pieces):
+            piece = slice(p * kp * line, (p + 1) * kp * line)
+            arrived = torch.cuda.Event()
+            with torch.cuda.stream(self.s_in):
+                shared_dev[piece].copy_(shared_host[piece], non_blocking=True)
+                arrived.record(self.s_in)
+            self.s_run.wait_event(arrived)
+            if self.col_c:      # A column-major: K piece = columns of A; B chunk column-major: K piece = rows of B
+                a = (_address(args.ref_A[0]) + p * kp * self.lda * es, self.lda)
+                b = (_address(args.ref_B[0]) + p * kp * es, self.ldb)
+            else:               # A chunk row-major: K piece = columns of A; B row-major: K piece = rows of B
+                a = (_address(args.ref_A[0]) + p * kp * es, self.lda)
+                b = (_address(args.ref_B[0]) + p * kp * self.ldb * es, self.ldb)
+            first, last = p == 0, p == self.k_pieces - 1
+            c = args.ref_C if first else args.ref_D
+            beta = self.beta if first else self.op.mul_identity
+            piece_args = Arguments((m, n, kp), a, b, c, args.ref_D, (self.alpha, beta))
+            self._launch(piece_args, extras if last else [], f"K piece {p} of chunk 0")
+
     def __call__(self, hA, hB, hC, hD, stream=None) -> None:
         """hA, hB, hC: pinned host tensors (flat storage, leading dimension = contiguous extent); hD receives the
         result.  Work is ordered after `stream` (default: the current stream) and `stream` waits for its end."""
@@ -80,28 +129,32 @@ class HostSrgemm:
             s.wait_event(start)
         shared_dev, shared_host = (self.dA, hA) if self.col_c else (self.dB, hB)
         moving_dev, moving_host = (self.dB, hB) if self.col_c else (self.dA, hA)
-        with torch.cuda.stream(self.s_in):
-            shared_dev.copy_(shared_host, non_blocking=True)
+        if self.workspace is None:
+            # one optional workspace for every launch shape of the pipeline (whole chunks and K pieces of chunk 0)
+            whole = self._chunk_args(0)[0]
+            (cm, cn, ck) = whole.problem_size
+            shapes = [whole, Arguments((cm, cn, ck // self.k_pieces), whole.ref_A, whole.ref_B, whole.ref_C,
+                                       whole.ref_D, whole.epilogue)]
+            need = max(self.op.get_optional_workspace_size(a) for a in shapes)
+            self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=self.device)
+        if self.k_pieces == 1:
+            with torch.cuda.stream(self.s_in):
+                shared_dev.copy_(shared_host, non_blocking=True)
         for j in range(self.chunks):
             args, moving, out = self._chunk_args(j)
-            arrived, done = torch.cuda.Event(), torch.cuda.Event()
             with torch.cuda.stream(self.s_in):
                 moving_dev[moving].copy_(moving_host[moving], non_blocking=True)
                 self.dC[out].copy_(hC[out], non_blocking=True)
+            extras = self.extra(j, out.start * self.es) if self.extra else []
+            done = torch.cuda.Event()
+            if j == 0 and self.k_pieces > 1:
+                self._first_chunk_by_k_pieces(args, shared_dev, shared_host, extras)
+            else:
+                arrived = torch.cuda.Event()
                 arrived.record(self.s_in)
-            self.s_run.wait_event(arrived)
-            with torch.cuda.stream(self.s_run):
-                if self.workspace is None:
-                    need = self.op.get_optional_workspace_size(args)
-                    self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=self.device)
-                st = self.op.initialize(args, self.workspace, self.s_run)
-                if st == Status.kSuccess:
-                    extras = self.extra(j, out.start * self.es) if self.extra else []
-                    st = self.op.run_push(extras, self.s_run) if extras else self.op.run(self.s_run)
-                if st != Status.kSuccess:
-                    raise RuntimeError(f"SRGEMM failed on chunk {j}: {st!r}")
-                self.launches += 1
-                done.record(self.s_run)
+                self.s_run.wait_event(arrived)
+                self._launch(args, extras, f"chunk {j}")
+            done.record(self.s_run)
             self.s_out.wait_event(done)
             with torch.cuda.stream(self.s_out):
                 hD[out].copy_(self.dD[out], non_blocking=True)

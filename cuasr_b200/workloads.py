@@ -29,7 +29,7 @@ class Workload:
     n: int
     k: int
     layouts: Tuple[Layout, Layout, Layout]
-    fill: str                      # "uniform", "graph", "words"
+    fill: str                      # "uniform", "graph", "apsp", "ints", "words"
     lo: float = 0.0
     hi: float = 1.0
     density: float = 1.0           # "graph": probability that an entry is present
@@ -52,6 +52,9 @@ class Workload:
         if self.fill == "uniform":
             fn = datagen.uniform_f32 if self.dtype == DType.F32 else datagen.uniform_f64
             return fn(seed, count, self.lo, self.hi, device=device, start=start)
+        if self.fill == "ints":
+            # whole numbers in [lo, hi): sums stay far from the 32-bit range, so nothing wraps on either side
+            return datagen.uniform_f32(seed, count, self.lo, self.hi, device=device, start=start).to(TORCH_DTYPE[self.dtype])
         if self.fill == "words":
             return datagen.words_u32(seed, count, device=device, start=start)
         if self.fill == "apsp":
@@ -106,6 +109,8 @@ WORKLOADS = {w.name: w for w in [
              description="config 5: max-min fp32, values uniform [0, 1)"),
     Workload("plustimes_f64_4096", "plus_multiplies", DType.F64, 4096, 4096, 4096, (COL, COL, COL), "uniform", -1.0, 1.0,
              alpha=1.0, beta=1.0, description="config 5: plus-times fp64, values uniform [-1, 1)"),
+    Workload("minplus_s32_4096", "minimum_plus", DType.S32, 4096, 4096, 4096, (COL, COL, COL), "ints", 0.0, 1000.0,
+             description="min-plus over 32-bit integers (one fused add-min instruction per product), values 0..999"),
     Workload("xorand_u32_4096", "bit_xor_bit_and", DType.U32, 4096, 4096, 4096, (COL, COL, COL), "words",
              alpha=-1, beta=-1, description="config 5: xor-and over uniform 32-bit words"),
 ]}

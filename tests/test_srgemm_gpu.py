@@ -119,6 +119,20 @@ def test_committed_reference_outputs_on_device(cuda_device):
     assert device_status() == 0
 
 
+@pytest.mark.parametrize("dt", [DType.S32, DType.U32])
+@pytest.mark.parametrize("ring", ["minimum_plus", "maximum_plus", "minimum_maximum", "maximum_minimum"])
+def test_integer_tropical_rings_take_the_tma_kernel(cuda_device, ring, dt):
+    """32-bit integer tropical and bottleneck rings run on the TMA kernel when K is a multiple of its K step (there
+    is no padding value for them); min-plus and max-plus use the fused add-min / add-max instructions."""
+    rng = np.random.default_rng(7)
+    kernels = set()
+    for layouts in util.ALL_LAYOUTS:
+        for mnk in ((260, 392, 96), (132, 516, 64), (128, 128, 32)):
+            kernels.add(_check(ring, dt, layouts, mnk, rng, beta_is_identity=True))
+    assert device_status() == 0
+    assert kernels == {"tma"}, kernels
+
+
 @pytest.mark.parametrize("ring", ["minimum_plus", "maximum_minimum", "plus_multiplies"])
 def test_submatrix_views(cuda_device, ring):
     """Operands that are windows of larger matrices: ld > extent and offset base pointers, as in
@@ -240,6 +254,9 @@ def test_host_buffer_pipeline_equals_one_shot(cuda_device, layouts):
         assert np.array_equal(hD.numpy(), want)
     chunked = layouts in ((COL, COL, COL), (ROW, COL, ROW), (ROW, ROW, ROW))
     assert pipe.chunks == (4 if chunked else 1)
+    # the first chunk runs as K pieces where the K range of the shared operand is a run of whole storage lines
+    assert pipe.k_pieces == (4 if layouts in ((COL, COL, COL), (ROW, ROW, ROW)) else 1)
+    assert HostSrgemm(Srgemm(*RINGS["plus_multiplies"], dt, *layouts), m, n, k, 1.0, 1.0, cuda_device).k_pieces == 1
     assert device_status() == 0
 
 
