@@ -257,12 +257,20 @@ struct ExtraOutputs {
 
 // Re-packing of MN-contiguous fp32 operands into K-contiguous scratch, so that the kernel variant with packed
 // fp32x2 adds (both operands deliver (k, k+1) register pairs) can run.  Worth it only for the rings that variant
-// speeds up, and only for problems large enough for the TMA kernel.
+// speeds up, for problems large enough for the TMA kernel, and when the copy is cheap against what it buys: the
+// variant saves about 2 % of the 2 m n k operations, the copy moves 8 bytes per re-packed element, which breaks even
+// near m n = 1000 x (re-packed rows).  A thin slice of a large product (one rank's share of a sharded SRGEMM, one
+// chunk of the host pipeline: 8192 x 1024 x 8192 measured 4.38 ms without and 4.50 ms with the copy) fails that test;
+// copies of less than 16 MB are always taken (512^3: 0.076 -> 0.050 ms).
 bool repack_pays(const cuasr_b200_desc_t& desc, const Normalised& p) {
   const bool ring = (desc.add_op == CUASR_OP_MINIMUM || desc.add_op == CUASR_OP_MAXIMUM) &&
                     (desc.mul_op == CUASR_OP_PLUS || desc.mul_op == CUASR_OP_MULTIPLIES);
-  return desc.dtype == CUASR_F32 && ring && static_cast<long long>(p.m) * p.n >= 256 * 256 && p.k >= 256 &&
-         (!p.a_kcontig || !p.b_kcontig);
+  if (!(desc.dtype == CUASR_F32 && ring && static_cast<long long>(p.m) * p.n >= 256 * 256 && p.k >= 256 &&
+        (!p.a_kcontig || !p.b_kcontig)))
+    return false;
+  const long long rows = (p.a_kcontig ? 0LL : p.m) + (p.b_kcontig ? 0LL : p.n);
+  const bool small_copy = rows * p.k < 4LL * 1024 * 1024;
+  return small_copy || static_cast<long long>(p.m) * p.n >= 2048LL * rows;
 }
 size_t repack_operand_bytes(int rows, int k) { return align_up(static_cast<size_t>(rows) * align_up(k, 4) * 4, 256); }
 size_t repack_bytes(const cuasr_b200_desc_t& desc, const Normalised& p) {
