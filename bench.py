@@ -324,7 +324,11 @@ def run_ours(args, wl):
     value = wl.ops / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the host-buffer call: pinned host operands in, D out, every step ----
-    hA = torch.empty(A.numel(), dtype=tdt).pin_memory(); hA.copy_(A)
+    # With several ranks every byte of A crosses a host link once per node: rank r brings the r-th part of A's
+    # storage from its pinned buffer and an NVLink all-gather completes A on every GPU.
+    a_part = A.numel() // world
+    a_mine = slice(rank * a_part, (rank + 1) * a_part)
+    hA = torch.empty(a_part, dtype=tdt).pin_memory(); hA.copy_(A[a_mine])
     hB = torch.empty(B.numel(), dtype=tdt).pin_memory(); hB.copy_(B)
     share = m * cols
     Cs, Ds = C[c0 * m: c0 * m + share], D[c0 * m: c0 * m + share]
@@ -338,11 +342,19 @@ def run_ours(args, wl):
     pipe = None
     if wl.split_k_slices == 1:
         extra_fn = (lambda j, byte_off: [p + off + byte_off for r, p in enumerate(peer_d) if r != rank]) if push else None
-        pipe = HostSrgemm(op, m, cols if world > 1 else n, k, wl.alpha, wl.beta, dev, chunks=8,
-                          extra_outputs_per_chunk=extra_fn, buffers=(A, B, Cs, Ds))
+        pipe = HostSrgemm(op, m, cols if world > 1 else n, k, wl.alpha, wl.beta, dev,
+                          chunks=8 if world == 1 else max(1, min(8, cols // 512)),
+                          extra_outputs_per_chunk=extra_fn, buffers=(A, B, Cs, Ds), shared_on_device=world > 1)
+
+    def bring_a():
+        A[a_mine].copy_(hA, non_blocking=True)
+        if world > 1:
+            dist.all_gather_into_tensor(A, A[a_mine])
 
     def e2e_step():
         if pipe is not None:
+            if world > 1:
+                bring_a()
             pipe(hA, hB, hC, hD, stream)
             if world > 1:
                 if push:
@@ -350,7 +362,7 @@ def run_ours(args, wl):
                 else:
                     dist.all_gather_into_tensor(D, Ds)
             return
-        A.copy_(hA, non_blocking=True); B.copy_(hB, non_blocking=True); Cs.copy_(hC, non_blocking=True)
+        bring_a(); B.copy_(hB, non_blocking=True); Cs.copy_(hC, non_blocking=True)
         if launch() != Status.kSuccess:
             raise RuntimeError("SRGEMM launch failed")
         gather()
@@ -368,8 +380,9 @@ def run_ours(args, wl):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t[0]) / e2e_steps
-    h2d = (hA.numel() + hB.numel() + hC.numel()) * es
-    d2h = hD.numel() * es
+    # bytes of the whole job per step: every rank's part of A, its columns of B and C in, its columns of D out
+    h2d = (hA.numel() + hB.numel() + hC.numel()) * es * world
+    d2h = hD.numel() * es * world
 
     # ---- rank 0: spot check against the CPU oracle, CPU baseline, JSON line ----
     if rank == 0:

@@ -29,7 +29,9 @@ def _address(ref) -> int:
 
 class HostSrgemm:
     def __init__(self, operator: Srgemm, m: int, n: int, k: int, alpha, beta, device, chunks: int = 8,
-                 extra_outputs_per_chunk=None, buffers=None):
+                 extra_outputs_per_chunk=None, buffers=None, shared_on_device: bool = False):
+        """shared_on_device: the operand every chunk needs (A for a column-major D) is already in its device buffer
+        when the call starts (for instance assembled from the ranks' pieces over NVLink); it is not copied here."""
         import torch
 
         self.torch = torch
@@ -63,6 +65,9 @@ class HostSrgemm:
         shared_lines_are_k = (col_c and la == Layout.COLUMN_MAJOR) or (not col_c and lb == Layout.ROW_MAJOR)
         exact = not (operator.add_op == Op.PLUS and operator.dtype in (DType.F32, DType.F64))
         self.k_pieces = 4 if (self.chunkable and shared_lines_are_k and exact and k % 4 == 0 and k >= 512) else 1
+        self.shared_on_device = bool(shared_on_device)
+        if self.shared_on_device:
+            self.k_pieces = 1
 
     def _chunk_args(self, j: int):
         """Arguments of chunk j and the element ranges of B (or A), C and D it touches."""
@@ -137,7 +142,7 @@ class HostSrgemm:
                                        whole.ref_D, whole.epilogue)]
             need = max(self.op.get_optional_workspace_size(a) for a in shapes)
             self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=self.device)
-        if self.k_pieces == 1:
+        if self.k_pieces == 1 and not self.shared_on_device:
             with torch.cuda.stream(self.s_in):
                 shared_dev.copy_(shared_host, non_blocking=True)
         for j in range(self.chunks):
