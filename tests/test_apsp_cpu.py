@@ -1,5 +1,6 @@
-"""Host logic of the sharded repeated-squaring solve (cuasr_b200/apsp.py) on CPU: two gloo ranks, with the CPU
-oracle standing in for the device SRGEMM and a gloo all-gather for the exchange."""
+"""Host logic of the sharded APSP solves (cuasr_b200/apsp.py) on CPU: two gloo ranks, with the CPU oracle standing
+in for the device SRGEMM; a gloo all-gather (repeated squaring) or broadcast (blocked Floyd-Warshall) for the
+exchange."""
 import os
 import socket
 
@@ -105,3 +106,68 @@ def test_graph_generator_blocks_match_the_whole():
     present = m[~torch.eye(n, dtype=torch.bool)]
     present = present[torch.isfinite(present)]
     assert present.min() >= 1 and present.max() <= 100 and torch.all(present == present.round())
+
+
+# ---- blocked Floyd-Warshall over ranks: ownership, look-ahead and panel rotation on CPU -----------------------
+def _host_floyd_warshall_class():
+    from cuasr_b200.apsp import BlockedFloydWarshall
+
+    _, fn = oracle._load(oracle.ORACLE_PATH, "cuasr_oracle_srgemm")
+    zero, inf = np.zeros(1, np.float32), np.full(1, np.inf, np.float32)
+
+    class HostFloydWarshall(BlockedFloydWarshall):
+        """The multi-rank driver unchanged, with the CPU oracle as the block product: its "device addresses" are
+        addresses of CPU tensors here.  Broadcast mode only (the push mode needs peer-mapped GPU memory)."""
+
+        def _srgemm(self, m, n, k, A, lda, B, ldb, C, ldc, D, ldd, extras=()):
+            assert not extras
+            st = fn(int(Op.MINIMUM), int(Op.PLUS), int(DType.F32), int(COL), int(COL), int(COL), m, n, k,
+                    zero.ctypes.data, A, lda, B, ldb, zero.ctypes.data, C, ldc, D, ldd, inf.ctypes.data, 1)
+            assert st == 0
+            self.launches += 1
+
+    return HostFloydWarshall
+
+
+def _fw_worker(rank, world, port, n, block, seed, distribution, look_ahead, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    solver = _host_floyd_warshall_class()(n, block, rank, world, "cpu", mode="allgather", distribution=distribution,
+                                          look_ahead=look_ahead)
+    solver.load_columns(torch.cat([random_graph(n, 0.05, seed, "cpu", rows=(kb * block, block))
+                                   for kb in solver.owned_blocks()]))
+    solver.solve()
+    solver.solve()        # the closure is a fixed point; the second solve re-uses every panel buffer
+    out[rank] = (solver.owned_blocks(), solver.result_columns().numpy().copy())
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("distribution,look_ahead", [("cyclic", True), ("cyclic", False), ("contiguous", True)])
+def test_blocked_floyd_warshall_two_ranks(distribution, look_ahead):
+    n, block, seed, world = 96, 16, 11, 2
+    out = mp.Manager().dict()
+    mp.spawn(_fw_worker, args=(world, _free_port(), n, block, seed, distribution, look_ahead, out), nprocs=world,
+             join=True)
+    flat = random_graph(n, 0.05, seed, "cpu").numpy()
+    want = floyd_warshall(flat.reshape(n, n).T).T.astype(np.float32).reshape(-1)       # column-major, like `flat`
+    blocks_seen = []
+    for rank in range(world):
+        blocks, cols = out[rank]
+        blocks_seen += blocks
+        mine = np.concatenate([want[kb * block * n:(kb + 1) * block * n] for kb in blocks])
+        assert np.array_equal(cols, mine), f"{distribution}: rank {rank}"
+    assert sorted(blocks_seen) == list(range(n // block))
+    expect0 = [0, 2, 4] if distribution == "cyclic" else [0, 1, 2]
+    assert out[0][0] == expect0
+
+
+def test_floyd_warshall_ownership_arithmetic():
+    cls = _host_floyd_warshall_class()
+    s = cls(64, 8, 1, 4, "cpu", mode="allgather")
+    assert s.owned_blocks() == [1, 5] and s.owner(6) == 2 and s.local_column(5) == 8 and s.look_ahead
+    c = cls(64, 8, 1, 4, "cpu", mode="allgather", distribution="contiguous")
+    assert c.owned_blocks() == [2, 3] and c.owner(6) == 3 and c.local_column(3) == 8
+    with pytest.raises(ValueError):
+        cls(64, 12, 0, 4, "cpu", mode="allgather")
+    with pytest.raises(ValueError):
+        cls(64, 8, 0, 4, "cpu", mode="allgather", distribution="random")
