@@ -3,15 +3,18 @@
 //   examples/00_minplus_srgemm/minplus_srgemm.cu:9-81           cuasr_minplus_srsgemm_nt_n (C aliases D)
 //   examples/01_userdefined_semiring/userdefined_semiring.cu:104-192   GF(2) SRGEMM with a user-defined xor functor
 //   examples/02_splitk_srgemm/splitk_srgemm.cu:17-103           cuasr_splitk_minplus_srsgemm_tn_t
+// plus an all-pairs-shortest-paths solve through the C entry points of cuasr_b200_apsp.h, from C++ alone.
 // Exit code 0 = every check passed.
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <limits>
 #include <random>
 #include <vector>
 
 #include <cuda_runtime.h>
 
+#include "cuasr_b200_apsp.h"
 #include "cuasr/functional.h"
 #include "cuasr/gemm/device/default_srgemm_configuration.h"
 #include "cuasr/gemm/device/srgemm.h"
@@ -185,6 +188,36 @@ int main() {
     ok = ok && gemm.run() == cutlass::Status::kErrorInternal;                         // run before initialize
     std::printf("status codes: %s\n", ok ? "ok" : "FAILED");
     failures += !ok;
+  }
+  {  // all-pairs shortest paths from C++ through the C entry points: both algorithms against a host Floyd-Warshall
+    const int n = 300, ld = 304;
+    std::bernoulli_distribution edge(0.03);
+    std::uniform_int_distribution<int> weight(1, 100);
+    const float inf = std::numeric_limits<float>::infinity();
+    std::vector<float> G(static_cast<size_t>(ld) * n, -1.0f);          // padding rows hold -1 and must stay
+    for (int j = 0; j < n; ++j)
+      for (int i = 0; i < n; ++i) G[i + static_cast<size_t>(j) * ld] = i == j ? 0.0f : edge(rng) ? float(weight(rng)) : inf;
+    std::vector<float> want = G;
+    for (int k = 0; k < n; ++k)
+      for (int j = 0; j < n; ++j)
+        for (int i = 0; i < n; ++i)
+          want[i + static_cast<size_t>(j) * ld] =
+              std::min(want[i + static_cast<size_t>(j) * ld], want[i + static_cast<size_t>(k) * ld] + want[k + static_cast<size_t>(j) * ld]);
+    for (int algorithm : {CUASR_APSP_REPEATED_SQUARING, CUASR_APSP_BLOCKED_FLOYD_WARSHALL}) {
+      float* dD = to_device(G);
+      cuasr_b200_apsp_args_t a{};
+      a.dtype = CUASR_F32; a.algorithm = algorithm; a.n = n; a.block = 64; a.D = dD; a.ldd = ld;
+      a.workspace_bytes = cuasr_b200_apsp_workspace_size(&a);
+      CHECK_CUDA(cudaMalloc(&a.workspace, a.workspace_bytes));
+      int st = cuasr_b200_apsp(&a);
+      CHECK_CUDA(cudaDeviceSynchronize());
+      std::vector<float> got(G.size());
+      CHECK_CUDA(cudaMemcpy(got.data(), dD, got.size() * sizeof(float), cudaMemcpyDeviceToHost));
+      bool ok = st == 0 && got == want && cuasr_b200_device_status(nullptr) == 0;
+      std::printf("cuasr_b200_apsp algorithm=%d: %s\n", algorithm, ok ? "ok" : "FAILED");
+      failures += !ok;
+      cudaFree(dD); cudaFree(a.workspace);
+    }
   }
   std::printf("%s\n", failures == 0 ? "ALL OK" : "FAILURES");
   return failures == 0 ? 0 : 1;
