@@ -79,6 +79,14 @@ class Srgemm {
   static int const kAlignmentA = AlignmentA;
   static int const kAlignmentB = AlignmentB;
   static bool const kSplitKSerial = SplitKSerial;
+  static int const kAlignmentC = EpilogueOutputOp::kCount;
+  // The reference's test bed and bench harness name the epilogue functor through the kernel type
+  // (test/device/testbed.h:52-54, bench/device/harness.h:49-50); there is no kernel type here, only that path.
+  struct SrgemmKernel {
+    struct Epilogue {
+      using OutputOp = EpilogueOutputOp;
+    };
+  };
 
   static_assert(std::is_same<ElementA, ElementC>::value && std::is_same<ElementB, ElementC>::value &&
                     std::is_same<ElementAccumulator, ElementC>::value,
