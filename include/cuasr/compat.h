@@ -11,6 +11,9 @@
 #include "cutlass/tensor_ref.h"
 #include "cutlass/arch/arch.h"
 #include "cutlass/arch/mma.h"
+#ifdef __CUDACC__   // device intrinsics inside: only a CUDA compiler can read it
+#include "cutlass/gemm/threadblock/threadblock_swizzle.h"
+#endif
 #else
 
 #include <cstdint>
@@ -63,6 +66,14 @@ struct GemmShape {
   static int const kN = N;
   static int const kK = K;
 };
+// Names that code written against the reference passes as the ThreadblockSwizzle argument
+// (examples/01_userdefined_semiring/userdefined_semiring.cu:131-132); this library rasterises tiles itself.
+namespace threadblock {
+template <int N = 1> struct GemmIdentityThreadblockSwizzle {};
+struct GemmHorizontalThreadblockSwizzle {};
+template <int N = 1> struct GemmSplitKIdentityThreadblockSwizzle {};
+struct GemmSplitKHorizontalThreadblockSwizzle {};
+}  // namespace threadblock
 }  // namespace gemm
 
 // A pointer and one leading dimension, in elements.

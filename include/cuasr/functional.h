@@ -62,6 +62,38 @@ struct OpCode<Functor, decltype(void(Functor::kOpCode))> {
   static constexpr int value = Functor::kOpCode;
 };
 
+// A functor that neither carries kOpCode nor has an OpCode<> specialisation (for instance the hand-written
+// binary_xor of examples/01_userdefined_semiring/userdefined_semiring.cu:56-99, compiled unchanged) is recognised by
+// what it computes: evaluated on the host on three pairs of small values, the nine operators this library implements
+// all give different answers.  Returns -1 for anything else, which the library refuses as "not supported".
+template <typename Functor, typename T>
+inline int probe_op_code() {
+  Functor f;
+  const long long got[3] = {static_cast<long long>(f(T(3), T(5))), static_cast<long long>(f(T(0), T(5))),
+                            static_cast<long long>(f(T(6), T(3)))};
+  struct Row { int code; long long want[3]; bool integers_only; };
+  const Row table[] = {{CUASR_OP_PLUS, {8, 5, 9}, false},       {CUASR_OP_MULTIPLIES, {15, 0, 18}, false},
+                       {CUASR_OP_MINIMUM, {3, 0, 3}, false},    {CUASR_OP_MAXIMUM, {5, 5, 6}, false},
+                       {CUASR_OP_BINARY_AND, {1, 0, 1}, false}, {CUASR_OP_BINARY_OR, {1, 1, 1}, false},
+                       {CUASR_OP_BIT_AND, {1, 0, 2}, true},     {CUASR_OP_BIT_OR, {7, 5, 7}, true},
+                       {CUASR_OP_BIT_XOR, {6, 5, 5}, true}};
+  for (const Row& row : table)
+    if ((!row.integers_only || std::is_integral<T>::value) && got[0] == row.want[0] && got[1] == row.want[1] &&
+        got[2] == row.want[2])
+      return row.code;
+  return -1;
+}
+
+// The operator code of any functor: declared (kOpCode or an OpCode<> specialisation) or, failing that, probed.
+template <typename Functor, typename T, typename = void>
+struct OpCodeOf {
+  static int get() { return probe_op_code<Functor, T>(); }
+};
+template <typename Functor, typename T>
+struct OpCodeOf<Functor, T, decltype(void(OpCode<Functor>::value))> {
+  static int get() { return OpCode<Functor>::value; }
+};
+
 template <typename T> struct DTypeCode;
 template <> struct DTypeCode<float>    { static constexpr int value = CUASR_F32; };
 template <> struct DTypeCode<double>   { static constexpr int value = CUASR_F64; };

@@ -162,8 +162,8 @@ class Srgemm {
  protected:
   static cuasr_b200_desc_t desc() {
     cuasr_b200_desc_t d;
-    d.add_op = OpCode<AdditionOp>::value;
-    d.mul_op = OpCode<MultiplicationOp>::value;
+    d.add_op = OpCodeOf<AdditionOp, ElementC>::get();
+    d.mul_op = OpCodeOf<MultiplicationOp, ElementC>::get();
     d.dtype = DTypeCode<ElementC>::value;
     d.layout_a = detail::LayoutCode<LayoutA>::value;
     d.layout_b = detail::LayoutCode<LayoutB>::value;

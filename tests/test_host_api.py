@@ -17,7 +17,10 @@ def test_can_implement_follows_the_reference_rules():
     assert op.can_implement(args()) == Status.kSuccess
     assert op.can_implement(args(slices=2)) == Status.kErrorInvalidProblem          # device/srgemm.h:198-200
     assert op.can_implement(args(m=0)) == Status.kErrorInvalidProblem
-    assert op.can_implement(args(lda=100)) == Status.kErrorInvalidProblem
+    # A and B are only read: a short leading dimension is an overlapping view, accepted like the reference does
+    assert op.can_implement(args(lda=100)) == Status.kSuccess
+    assert op.can_implement(args(lda=0)) == Status.kErrorInvalidProblem
+    assert op.can_implement(args(ldd=100)) == Status.kErrorInvalidProblem           # overlapping lines of D would race
     assert op.can_implement(args(a=P + 2)) == Status.kErrorMisalignedOperand
     assert op.can_implement(args(a=None)) == Status.kErrorInvalidProblem
     serial = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL, split_k_serial=True)
@@ -28,10 +31,12 @@ def test_can_implement_follows_the_reference_rules():
 
 def test_layout_decides_the_minimum_leading_dimension():
     op = Srgemm(Op.PLUS, Op.MULTIPLIES, DType.F64, ROW, COL, ROW)
-    # A is 100 x 300 row-major (ld >= 300), B is 300 x 50 column-major (ld >= 300), C is 100 x 50 row-major (ld >= 50)
+    # A is 100 x 300 row-major, B is 300 x 50 column-major, C and D are 100 x 50 row-major (ld >= 50)
     ok = args(m=100, n=50, k=300, lda=300, ldb=300, ldc=50, ldd=50, epilogue=(1.0, 0.0))
     assert op.can_implement(ok) == Status.kSuccess
-    assert op.can_implement(args(m=100, n=50, k=300, lda=299, ldb=300, ldc=50, ldd=50)) == Status.kErrorInvalidProblem
+    assert op.can_implement(args(m=100, n=50, k=300, lda=299, ldb=300, ldc=50, ldd=50)) == Status.kSuccess
+    assert op.can_implement(args(m=100, n=50, k=300, lda=300, ldb=300, ldc=49, ldd=50, epilogue=(1.0, 1.0))) \
+        == Status.kErrorInvalidProblem
     assert op.can_implement(args(m=100, n=50, k=300, lda=300, ldb=300, ldc=50, ldd=49)) == Status.kErrorInvalidProblem
     assert op.can_implement(args(m=100, n=50, k=300, lda=300, ldb=300, ldc=50, ldd=50, d=P + 4)) \
         == Status.kErrorMisalignedOperand                                              # 8-byte elements

@@ -260,6 +260,22 @@ def test_host_buffer_pipeline_equals_one_shot(cuda_device, layouts):
     assert device_status() == 0
 
 
+def test_overlapping_operand_views(cuda_device):
+    """A leading dimension shorter than the extent is an overlapping (sliding-window) view of a read-only operand;
+    the reference accepts it (its examples/02 passes one) and so does this library, with the host SRGEMM's answer."""
+    rng = np.random.default_rng(5)
+    dt, ring = DType.F32, "minimum_plus"
+    m, n, k = 96, 80, 200
+    for layouts, lda, ldb in (((ROW, COL, ROW), 16, 8), ((COL, ROW, COL), 4, 12), ((ROW, COL, COL), 200, 8)):
+        A = rng.integers(-8, 9, size=m * k + k).astype(np.float32)          # large enough for every view below
+        B = rng.integers(-8, 9, size=n * k + k).astype(np.float32)
+        C, ldc = util.make_matrix(rng, dt, layouts[2], m, n)
+        want = util.run_oracle(ring, dt, layouts, (m, n, k), 0.0, A, lda, B, ldb, 0.0, C, ldc)
+        got, kernel = util.run_device(ring, dt, layouts, (m, n, k), 0.0, A, lda, B, ldb, 0.0, C, ldc)
+        assert np.array_equal(got, want) and kernel == "generic", (layouts, kernel)
+    assert device_status() == 0
+
+
 def test_plus_times_tolerance(cuda_device):
     """Plus-times on non-integer data: the device fuses multiply-add and sums in a different order, so the
     check is |got - want| <= 8 K eps (|A| |B|)_ij."""
@@ -307,7 +323,7 @@ def test_status_codes(cuda_device):
     assert op(big, ows) == Status.kSuccess and op.last_kernel() != "tma"
     # empty problem, short leading dimension, misaligned pointer, unsupported ring
     assert op.can_implement(Arguments((0, 64, 64), (x, 64), (x, 64), (x, 64), (x, 64))) == Status.kErrorInvalidProblem
-    assert op.can_implement(Arguments((64, 64, 64), (x, 32), (x, 64), (x, 64), (x, 64))) == Status.kErrorInvalidProblem
+    assert op.can_implement(Arguments((64, 64, 64), (x, 64), (x, 64), (x, 64), (x, 32))) == Status.kErrorInvalidProblem
     assert op.can_implement(Arguments((8, 8, 8), (x.data_ptr() + 2, 64), (x, 64), (x, 64), (x, 64))) \
         == Status.kErrorMisalignedOperand
     weird = Srgemm(Op.BIT_XOR, Op.BIT_AND, DType.F32, COL, COL, COL)
