@@ -11,6 +11,7 @@
 #include "cutlass/tensor_ref.h"
 #include "cutlass/arch/arch.h"
 #include "cutlass/arch/mma.h"
+#include "cutlass/numeric_conversion.h"   // the reference's device headers bring it in; its tools rely on that
 #ifdef __CUDACC__   // device intrinsics inside: only a CUDA compiler can read it
 #include "cutlass/gemm/threadblock/threadblock_swizzle.h"
 #endif

@@ -15,8 +15,11 @@ struct IdentityThreadblockSwizzle {};
 struct SplitKHorizontalThreadblockSwizzle {};
 
 template <typename ElementA, typename ElementB, typename ElementC, typename ElementAccumulator,
-          typename OperatorClass, typename AdditionOp, typename MultiplicationOp, typename ArchTag>
+          typename OperatorClass, typename AdditionOp_, typename MultiplicationOp_, typename ArchTag>
 struct DefaultSemiRingConfiguration {
+  // the ring the configuration was asked for (bench/device/simt_*_sm50.cu read these back)
+  using AdditionOp = AdditionOp_;
+  using MultiplicationOp = MultiplicationOp_;
   static int const kAlignmentA = 1;
   static int const kAlignmentB = 1;
   using ThreadblockShape = cutlass::gemm::GemmShape<128, 128, int(128 / sizeof(ElementA))>;
