@@ -33,6 +33,44 @@ def test_headers_compile_without_cutlass(tmp_path):
                     "-I", "/usr/local/cuda/include", str(src)], check=True)
 
 
+PROBE = r"""
+#include <cstdio>
+#include "cuasr/functional.h"
+// functors the headers know nothing about, in the shape of examples/01_userdefined_semiring/userdefined_semiring.cu:56-99
+template <typename T> struct my_xor  { static constexpr T Identity = 0; T operator()(T l, T const& r) const { return l ^ r; } };
+template <typename T> struct my_band { static constexpr T Identity = ~T(0); T operator()(T l, T const& r) const { return l & r; } };
+template <typename T> struct my_bor  { static constexpr T Identity = 0; T operator()(T l, T const& r) const { return l | r; } };
+template <typename T> struct my_min  { T operator()(T l, T const& r) const { return r < l ? r : l; } };
+template <typename T> struct my_max  { T operator()(T l, T const& r) const { return l < r ? r : l; } };
+template <typename T> struct my_add  { T operator()(T l, T const& r) const { return l + r; } };
+template <typename T> struct my_mul  { T operator()(T l, T const& r) const { return l * r; } };
+template <typename T> struct my_land { T operator()(T l, T const& r) const { return T(l && r); } };
+template <typename T> struct my_lor  { T operator()(T l, T const& r) const { return T(l || r); } };
+template <typename T> struct my_sub  { T operator()(T l, T const& r) const { return l - r; } };
+struct tagged { static constexpr int kOpCode = CUASR_OP_MAXIMUM; float operator()(float l, float const& r) const { return l - r; } };
+int main() {
+  int bad = 0;
+#define EXPECT(F, T, CODE) if (cuasr::OpCodeOf<F<T>, T>::get() != (CODE)) { std::printf("%s<%s>\n", #F, #T); ++bad; }
+  EXPECT(my_xor, int, CUASR_OP_BIT_XOR)   EXPECT(my_band, unsigned, CUASR_OP_BIT_AND)  EXPECT(my_bor, int, CUASR_OP_BIT_OR)
+  EXPECT(my_min, float, CUASR_OP_MINIMUM) EXPECT(my_max, double, CUASR_OP_MAXIMUM)     EXPECT(my_add, float, CUASR_OP_PLUS)
+  EXPECT(my_mul, double, CUASR_OP_MULTIPLIES) EXPECT(my_land, int, CUASR_OP_BINARY_AND) EXPECT(my_lor, float, CUASR_OP_BINARY_OR)
+  EXPECT(my_min, int, CUASR_OP_MINIMUM)   EXPECT(my_sub, float, -1)                    EXPECT(my_sub, int, -1)
+  EXPECT(cuasr::minimum, float, CUASR_OP_MINIMUM)                                      // declared functors are not probed
+  if (cuasr::OpCodeOf<tagged, float>::get() != CUASR_OP_MAXIMUM) ++bad;               // kOpCode wins over behaviour
+  return bad;
+}
+"""
+
+
+def test_undeclared_functors_are_recognised_by_what_they_compute(tmp_path):
+    src, exe = tmp_path / "probe.cpp", tmp_path / "probe"
+    src.write_text(PROBE)
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include",
+                    str(src), "-o", str(exe)], check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout
+
+
 @pytest.mark.gpu
 def test_rehosted_reference_examples(cuda_device):
     assert os.path.exists(BINARY), "build it with __graft_entry__.build()"
