@@ -37,7 +37,8 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons while the timed region runs: through NVML every 10 ms where it is
+    available, else by polling nvidia-smi."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -45,16 +46,57 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index, self.samples, self._stop, self._thread = index, [], threading.Event(), None
 
+    def _nvml(self):
+        """(module, handle) for this process's GPU `index` through NVML, or None where NVML cannot be used (then
+        nvidia-smi is polled instead).  Reading only: no setting of the GPU is touched."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = None
+            try:        # CUDA's device order need not be NVML's: go by UUID where torch knows it
+                import torch
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+                for candidate in (uuid, uuid.encode()):
+                    try:
+                        handle = pynvml.nvmlDeviceGetHandleByUUID(candidate)
+                        break
+                    except Exception:
+                        continue
+            except Exception:
+                handle = None
+            if handle is None:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)      # fails here if the handle is unusable
+            return pynvml, handle
+        except Exception:
+            return None
+
+    def _sample_nvml(self, nvml, handle):
+        sm = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+        top = nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)
+        reasons = getattr(nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            nvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        mask = int(reasons(handle))
+        # bits of the NVML reasons mask: software power cap 0x4, hardware slowdown 0x8, software thermal 0x20,
+        # hardware thermal 0x40
+        flag = lambda bit: "Active" if mask & bit else "Not Active"
+        return [str(sm), str(top), flag(0x8), flag(0x40), flag(0x20), flag(0x4)]
+
     def _run(self):
+        nvml = self._nvml()
         while not self._stop.is_set():
             try:
+                if nvml is not None:
+                    self.samples.append(self._sample_nvml(*nvml))
+                    self._stop.wait(0.01)
+                    continue
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
                                       "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
                 parts = [p.strip() for p in out.strip().split(",")]
                 if len(parts) == 6:
                     self.samples.append(parts)
             except Exception:
-                pass
+                nvml = None             # an NVML call failed mid-run: fall back to polling nvidia-smi
             self._stop.wait(0.1)
 
     def __enter__(self):
