@@ -47,3 +47,13 @@ def test_struct_layout_matches_the_header():
     # int32 x 8 ; int32 x 4 + 4 x (ptr, int64) + 4 x 8-byte scalars + ptr + size_t + ptr
     assert ctypes.sizeof(_lib.Desc) == 32
     assert ctypes.sizeof(_lib.Args) == 16 + 4 * 16 + 4 * 8 + 24
+
+
+def test_headers_are_plain_c(tmp_path):
+    """The boundary is a C ABI: both public headers must compile as C11 on their own."""
+    import subprocess
+    for header in ("cuasr_b200.h", "cuasr_b200_apsp.h", "cuasr_b200_types.h"):
+        src = tmp_path / (header + ".c")
+        src.write_text(f'#include "{header}"\nint main(void) {{ return 0; }}\n')
+        subprocess.run(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), str(src)],
+                       check=True)
