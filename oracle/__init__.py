@@ -21,6 +21,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_PATH = os.path.join(_HERE, "libcuasr_oracle.so")
 REF_PATH = os.path.join(_HERE, "_ref", "libcuasr_ref.so")
 REF_DEVICE_PATH = os.path.join(_HERE, "_ref", "libcuasr_ref_device.so")
+REF_PATH_PATH = os.path.join(_HERE, "_ref", "libcuasr_ref_path.so")
 
 _ARGTYPES = [ctypes.c_int] * 9 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
                                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
@@ -61,6 +62,26 @@ def ref_device_srgemm(add_op, mul_op, dtype, mnk, A, lda, B, ldb, C, ldc, D, ldd
     al, be = (np.array([v], dtype=np_t) for v in (alpha, beta))
     return int(fn(int(add_op), int(mul_op), int(dtype), int(mnk[0]), int(mnk[1]), int(mnk[2]), int(A), int(lda),
                   int(B), int(ldb), int(C), int(ldc), int(D), int(ldd), al.ctypes.data, be.ctypes.data, int(stream)))
+
+
+def have_ref_path() -> bool:
+    return os.path.exists(REF_PATH_PATH)
+
+
+def ref_fwgemm(A, B, dist, parent, n: int):
+    """The reference's legacy cpu_fwgemm_naive (oracle/_ref/libcuasr_ref_path.so) on square column-major n x n
+    matrices, in place: dist <- min(dist, A (x) B), parent <- index of the improving k.  float32 or float64 data,
+    int32 parent; returns (dist, parent)."""
+    lib = ctypes.CDLL(REF_PATH_PATH)
+    fn = lib.cuasr_ref_fwgemm
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                   ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    assert parent.dtype == np.int32 and A.dtype == B.dtype == dist.dtype and dist.dtype in (np.float32, np.float64)
+    for arr in (A, B, dist, parent):
+        assert arr.flags["C_CONTIGUOUS"] and arr.size == n * n
+    fn(int(dist.dtype == np.float64), n, A.ctypes.data, n, B.ctypes.data, n, dist.ctypes.data, n, parent.ctypes.data)
+    return dist, parent
 
 
 def max_threads(ref: bool = False) -> int:

@@ -195,8 +195,11 @@ int cuasr_oracle_max_threads(void) {
  * parent to k (so ties keep the earlier k, and an entry that is never improved keeps its old parent).
  * Generalised from the reference's square, column-major, min-only form to M x N x K, both layouts, and max-plus;
  * k_offset is added to the recorded index (for callers that work on a K-block of a larger product).
- * Parity status: the reference holds no test or fixture for this routine (it is never called there), so the
- * parent output is UNPINNED against the reference; the distance output is pinned through cuasr_oracle_srgemm.
+ * Parity status: PINNED.  The reference holds no test or fixture for this routine (it is never called there), so
+ * the routine itself is the anchor: compiled unmodified (oracle/ref_path.cpp -> oracle/_ref/libcuasr_ref_path.so),
+ * its distances and parents on square column-major inputs full of ties are committed as
+ * tests/golden/fwgemm_outputs.npz and this restatement must reproduce them; the generalisations (M x N x K, row-major,
+ * max-plus, k_offset) have no reference counterpart and are checked against the SRGEMM oracle's distances.
  */
 #define DEFINE_PATH(NAME, T)                                                                            \
   static void NAME(int M, int N, int K, const T *A, int rmA, int lda, const T *B, int rmB, int ldb,     \

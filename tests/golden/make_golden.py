@@ -9,6 +9,9 @@ Writes
   host_srgemm_outputs.npz     outputs of the reference's own host_srgemm.h (oracle/_ref) for every ring,
                               element type and layout combination on seeded small-integer inputs, with the
                               inputs, so that the fixtures do not depend on any random generator
+  fwgemm_outputs.npz          outputs (distances and parents) of the reference's legacy path-tracking routine
+                              test/regress/include/fwgpu/cpu_srgemm.hpp (oracle/_ref, `make -C oracle refpath`) on
+                              square column-major inputs with many ties, with the inputs
 """
 import json
 import os
@@ -62,6 +65,24 @@ def host_outputs():
     return store
 
 
+def fwgemm_outputs():
+    rng = np.random.default_rng(1905)
+    store = {}
+    for np_t, tag in ((np.float32, "f32"), (np.float64, "f64")):
+        for n in (5, 17, 64):
+            # small integers: many equal candidates, so "which k wins a tie" is exercised, and every sum is exact
+            A = rng.integers(0, 6, size=n * n).astype(np_t)
+            B = rng.integers(0, 6, size=n * n).astype(np_t)
+            dist = rng.integers(0, 9, size=n * n).astype(np_t)      # zeros and ones often stay unimproved
+            parent = rng.integers(-5, 0, size=n * n).astype(np.int32)
+            key = f"{tag}|{n}"
+            store[key + "|A"], store[key + "|B"] = A.astype(np.int8), B.astype(np.int8)
+            store[key + "|dist_in"], store[key + "|parent_in"] = dist.astype(np.int8), parent.astype(np.int8)
+            d, p = oracle.ref_fwgemm(A, B, dist.copy(), parent.copy(), n)
+            store[key + "|dist_out"], store[key + "|parent_out"] = d, p
+    return store
+
+
 def main():
     reference = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CUASR_REFERENCE", "/root/reference")
     assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref"
@@ -70,6 +91,8 @@ def main():
     store = host_outputs()
     np.savez_compressed(os.path.join(HERE, "host_srgemm_outputs.npz"), **store)
     print(len(store) // 5, "input sets written")
+    assert oracle.have_ref_path(), "build the path checker first: make -C oracle refpath"
+    np.savez_compressed(os.path.join(HERE, "fwgemm_outputs.npz"), **fwgemm_outputs())
 
 
 if __name__ == "__main__":

@@ -29,3 +29,15 @@ def host_cases():
             "A": z[key + "|A"].astype(np_t), "B": z[key + "|B"].astype(np_t), "C": z[key + "|C"].astype(np_t),
             "D_ann": z[key + "|Dann"], "D_id": z[key + "|Did"],
         }
+
+
+def fwgemm_cases():
+    """Yields dicts: dtype (numpy), n, A, B, dist_in, parent_in, dist_out, parent_out of the reference's legacy
+    path-tracking routine (square, column-major)."""
+    z = np.load(os.path.join(GOLDEN, "fwgemm_outputs.npz"))
+    for key in sorted(k[:-2] for k in z.files if k.endswith("|A")):
+        tag, n = key.split("|")
+        np_t = np.float32 if tag == "f32" else np.float64
+        yield {"key": key, "dtype": np_t, "n": int(n), "A": z[key + "|A"].astype(np_t), "B": z[key + "|B"].astype(np_t),
+               "dist_in": z[key + "|dist_in"].astype(np_t), "parent_in": z[key + "|parent_in"].astype(np.int32),
+               "dist_out": z[key + "|dist_out"], "parent_out": z[key + "|parent_out"]}

@@ -34,6 +34,51 @@ def test_oracle_path_distances_equal_the_pinned_srgemm_oracle():
                 assert Dm[i, j] == Cm[i, j]
 
 
+def test_oracle_path_equals_the_reference_routine_on_committed_outputs():
+    """Distances AND parents of the path oracle against outputs of the reference's own cpu_fwgemm_naive
+    (tests/golden/fwgemm_outputs.npz, written by tests/golden/make_golden.py): inputs full of ties."""
+    import golden_io
+    cases = list(golden_io.fwgemm_cases())
+    assert len(cases) == 6
+    for c in cases:
+        n, dt = c["n"], (DType.F32 if c["dtype"] == np.float32 else DType.F64)
+        dist, parent = oracle.srgemm_path(dt, (COL, COL, COL), (n, n, n), c["A"], n, c["B"], n, c["dist_in"].copy(), n,
+                                          c["parent_in"].copy(), n)
+        assert np.array_equal(dist, c["dist_out"]), c["key"]
+        assert np.array_equal(parent, c["parent_out"]), c["key"]
+        assert (parent != c["parent_in"]).any() and (parent == c["parent_in"]).any()     # both branches occur
+
+
+@pytest.mark.skipif(not oracle.have_ref_path(), reason="oracle/_ref/libcuasr_ref_path.so was not built")
+def test_oracle_path_equals_the_reference_routine_live():
+    rng = np.random.default_rng(8)
+    for np_t, dt in ((np.float32, DType.F32), (np.float64, DType.F64)):
+        for n in (1, 7, 33, 96):
+            A = rng.integers(0, 5, n * n).astype(np_t)
+            B = rng.integers(0, 5, n * n).astype(np_t)
+            d0 = rng.integers(1, 8, n * n).astype(np_t)
+            p0 = np.full(n * n, -1, np.int32)
+            want_d, want_p = oracle.ref_fwgemm(A, B, d0.copy(), p0.copy(), n)
+            got_d, got_p = oracle.srgemm_path(dt, (COL, COL, COL), (n, n, n), A, n, B, n, d0.copy(), n, p0.copy(), n)
+            assert np.array_equal(got_d, want_d) and np.array_equal(got_p, want_p), (np_t.__name__, n)
+
+
+@pytest.mark.gpu
+def test_path_tracking_on_committed_reference_outputs(cuda_device):
+    """The device kernel against the same committed outputs of the reference's routine."""
+    import golden_io
+    import torch
+    for c in golden_io.fwgemm_cases():
+        n, dt = c["n"], (DType.F32 if c["dtype"] == np.float32 else DType.F64)
+        dA, dB = torch.from_numpy(c["A"]).cuda(), torch.from_numpy(c["B"]).cuda()
+        dD, dP = torch.from_numpy(c["dist_in"].copy()).cuda(), torch.from_numpy(c["parent_in"].copy()).cuda()
+        op = Srgemm(Op.MINIMUM, Op.PLUS, dt, COL, COL, COL)
+        assert srgemm_path(op, (n, n, n), (dA, n), (dB, n), (dD, n), (dP, n)) == Status.kSuccess
+        torch.cuda.synchronize()
+        assert np.array_equal(dD.cpu().numpy(), c["dist_out"]) and np.array_equal(dP.cpu().numpy(), c["parent_out"]), c["key"]
+    assert device_status() == 0
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("dt", [DType.F32, DType.F64])
 @pytest.mark.parametrize("maximize", [False, True])
