@@ -36,6 +36,18 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0}, "fallback"
 
 
+def dram_traffic(workload: str):
+    """Bytes one launch of `workload` moved to and from DRAM in the committed ncu capture (None when there is none).
+    The figures live in one tracked table beside the profile summaries so that this file and they cannot drift."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            entry = json.load(f).get(workload)
+        return int(entry["bytes_per_launch"]) if entry else None
+    except (OSError, ValueError, KeyError):
+        return None
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons while the timed region runs: through NVML every 10 ms where it is
     available, else by polling nvidia-smi."""
@@ -118,6 +130,15 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
+def host_threads() -> int:
+    """Host threads the CPU arm uses: the cores this process may run on.  OpenMP's own default is not used because
+    launchers such as torchrun export OMP_NUM_THREADS=1 to every rank."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def identity_of(wl):
     from cuasr_b200 import RINGS, identity
     return identity(RINGS[wl.ring][0], wl.dtype) if wl.add_identity is None else wl.add_identity
@@ -161,7 +182,7 @@ def cpu_run(wl, lines: int, repeats: int = 1, warmup: int = 0):
 
     use_ref = oracle.have_ref()
     fn = oracle.ref_srgemm if use_ref else oracle.srgemm
-    cores = oracle.max_threads(use_ref)
+    cores = host_threads()
     mnk, A, lda, B, ldb, C, ldc = cpu_sample(wl, lines)
     D = np.empty_like(C)
     add_op, mul_op = RINGS[wl.ring]
@@ -426,6 +447,12 @@ def run_ours(args, wl):
     h2d = (hA.numel() + hB.numel() + hC.numel()) * es * world
     d2h = hD.numel() * es * world
 
+    # ---- the north star's second metric, at every N: the whole n = 16384 APSP solve, sharded over the ranks ----
+    apsp_rec = None
+    if wl.name == "minplus_f32_8192" and not args.no_apsp:
+        from cuasr_b200.workloads import WORKLOADS
+        apsp_rec = apsp_solve_record(WORKLOADS["apsp_16384"], rank, world, dev, args.exchange)
+
     # ---- rank 0: spot check against the CPU oracle, CPU baseline, JSON line ----
     if rank == 0:
         _, _, _, _, want = cpu_run(wl, 32)
@@ -469,20 +496,91 @@ def run_ours(args, wl):
             "roofline": {"bound": "CUDA cores (issue / register-file ports); HBM is orders of magnitude below",
                          "achieved": round(achieved, 3), "peak": round(peak_tops, 2), "unit": "TOP/s",
                          "frac": round(achieved / peak_tops, 4),
+                         # against one semiring operation per lane per clock (half the FP32-FMA line): the ceiling
+                         # of any formulation that spends one issued lane-instruction per operation
+                         "achieved_vs_1op_per_lane_clk": round(achieved / (peak_tops / 2), 4),
                          "peak_source": f"{sms} SMs x 128 lanes x 2 x sm_max_mhz ({peak_kind} clock {peaks['sm_max_mhz']:.0f} MHz)",
                          "kernel_ms": round(kernel_ms, 4),
                          "hbm_achieved_gbs": round(algorithmic_bytes / (kernel_ms * 1e-3) / 1e9, 2),
                          "hbm_peak_gbs": peaks["hbm_gbs"],
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture
-                         # summarised in profiles/bench_minplus_f32_8192_launch_list_and_dram.md
-                         "traffic": 3757164032 if (wl.name == "minplus_f32_8192" and world == 1) else None},
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from an ncu capture
+                         "traffic": dram_traffic(wl.name) if world == 1 else None},
             "cpu_baseline": cpu,
             "reference_device_kernel": refdev,
             "parity_spot_check": parity,
+            "apsp_16384": apsp_rec,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def apsp_solve_record(wl, rank, world, dev, exchange):
+    """One whole sharded APSP solve by repeated squaring (ceil(log2 n) squarings of the graph of `wl`): the adjacency
+    matrix comes from pinned host memory, every rank's block of distances goes back.  Returns, on rank 0, seconds of
+    the squarings alone and end to end (device events, max over ranks) and a check of the last squaring against the
+    host SRGEMM; None on the other ranks."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from cuasr_b200 import DType, Layout, Op, device_status
+    from cuasr_b200.apsp import CudaBackend, ShardedSquaring
+
+    n = wl.n
+    squarings = ShardedSquaring.squarings_needed(n)
+    backend = CudaBackend(n, rank, world, dev, mode=exchange)
+    solver = ShardedSquaring(n, rank, world, backend)
+    stream = torch.cuda.current_stream()
+    host_in = torch.empty(n * n, dtype=torch.float32).pin_memory()
+    host_in.copy_(wl.operand("A", dev))
+    host_out = torch.empty(n * n // world, dtype=torch.float32).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    backend.bufs[0].copy_(host_in, non_blocking=True)
+    solver.step()                                   # warm-up: workspace allocation, first-launch costs
+    barrier()
+    e0, k0, k1, e1 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+    solver.cur, solver.nxt = 0, 1
+    e0.record(stream)
+    backend.bufs[0].copy_(host_in, non_blocking=True)
+    k0.record(stream)
+    for _ in range(squarings - 1):
+        solver.step()
+    k1.record(stream)
+    before_last = backend.matrix(solver.cur).clone()
+    k2, k3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k2.record(stream)
+    solver.step()
+    k3.record(stream)
+    mine = backend.matrix(solver.cur)[solver.c0 * n:(solver.c0 + solver.cols) * n]
+    host_out.copy_(mine, non_blocking=True)
+    e1.record(stream)
+    barrier()
+    clone_ms = k1.elapsed_time(k2)                 # the copy kept for the check is not part of the solve
+    t = torch.tensor([k0.elapsed_time(k1) + k2.elapsed_time(k3), e0.elapsed_time(e1) - clone_ms],
+                     dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ok = device_status() == 0
+    if rank != 0:
+        return None
+    src = before_last.cpu().numpy()
+    blk = np.ascontiguousarray(src[: 32 * n])
+    want = np.empty(32 * n, np.float32)
+    fn = oracle.ref_srgemm if oracle.have_ref() else oracle.srgemm
+    col = Layout.COLUMN_MAJOR
+    fn(Op.MINIMUM, Op.PLUS, DType.F32, (col, col, col), (n, 32, n), 0.0, src, n, blk, n, 0.0, blk, n, want, n,
+       np.float32(np.inf), host_threads())
+    return {"n": n, "squarings": squarings, "seconds": round(float(t[0]) * 1e-3, 4),
+            "seconds_end_to_end": round(float(t[1]) * 1e-3, 4), "exchange": exchange if world > 1 else "none",
+            "sharding": f"{n // world} columns of D per rank",
+            "parity_spot_check": bool(ok and np.array_equal(host_out.numpy()[: 32 * n], want))}
 
 
 def run_apsp_fw(args, wl):
@@ -549,20 +647,35 @@ def run_apsp_fw(args, wl):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
+    # fixed point, at every world size: one more min-plus step over sampled columns must change nothing (checked by
+    # the host SRGEMM on rank 0).  With several ranks the distributed result is first gathered over NCCL.
+    blocks_of = lambda r: [kb for kb in range(n // block) if solver.owner(kb) == r]
+    if world > 1:
+        gathered = torch.empty(world * cols * n, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(gathered, solver.D)
+    else:
+        gathered = solver.D
+    parity = None
     if rank == 0:
-        # fixed point: one more min-plus step over 32 of my columns must change nothing (checked on the CPU oracle)
         import oracle
         from cuasr_b200 import DType, Layout, Op
-        parity = None
-        if world == 1:
-            full = host_out.numpy()
-            blk = np.ascontiguousarray(full[: 32 * n])
+        full_dev = torch.empty(n * n, dtype=torch.float32, device=dev)
+        for r in range(world):
+            for i, kb in enumerate(blocks_of(r)):
+                src = gathered[(r * cols + i * block) * n:(r * cols + (i + 1) * block) * n]
+                full_dev[kb * block * n:(kb + 1) * block * n].copy_(src)
+        full = full_dev.cpu().numpy()
+        del full_dev
+        fn = oracle.ref_srgemm if oracle.have_ref() else oracle.srgemm
+        col = Layout.COLUMN_MAJOR
+        parity = True
+        # the first columns (rank 0's), 32 in the middle, and the last (another rank's where there is one)
+        for c0 in sorted({0, (n // 2) // 32 * 32, n - 32}):
+            blk = np.ascontiguousarray(full[c0 * n:(c0 + 32) * n])
             again = np.empty_like(blk)
-            fn = oracle.ref_srgemm if oracle.have_ref() else oracle.srgemm
-            col = Layout.COLUMN_MAJOR
             fn(Op.MINIMUM, Op.PLUS, DType.F32, (col, col, col), (n, 32, n), 0.0, full, n, blk, n, 0.0, blk, n, again, n,
-               np.float32(np.inf), 0)
-            parity = bool(np.array_equal(again, blk))
+               np.float32(np.inf), host_threads())
+            parity = parity and bool(np.array_equal(again, blk))
         line = {
             "metric": "apsp_blocked_floyd_warshall_seconds", "value": round(ms * 1e-3, 5), "unit": "s", "n_gpus": world,
             "steps": args.steps, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(ms, 3),
@@ -666,10 +779,10 @@ def run_apsp(args, wl):
         col = Layout.COLUMN_MAJOR
         t0 = time.perf_counter()
         fn(Op.MINIMUM, Op.PLUS, DType.F32, (col, col, col), (n, 32, n), 0.0, src, n, blk, n, 0.0, blk, n, want, n,
-           np.float32(np.inf), 0)
+           np.float32(np.inf), host_threads())
         cpu_sec = time.perf_counter() - t0
         parity = bool(np.array_equal(host_out.numpy()[: 32 * n], want))
-        cores = oracle.max_threads(oracle.have_ref())
+        cores = host_threads()
         peaks, peak_kind = measured_peaks()
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         peak_tops = sms * 128 * 2 * peaks["sm_max_mhz"] * 1e6 / 1e12
@@ -712,6 +825,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="minplus_f32_8192")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--no-apsp", action="store_true",
+                    help="skip the n = 16384 APSP solve appended to the default workload's line (profiling runs)")
     ap.add_argument("--fw-block", type=int, default=0,
                     help="block size of the blocked Floyd-Warshall workload (0: 1024 up to 2 GPUs, 512 beyond)")
     ap.add_argument("--exchange", choices=("push", "allgather"), default="push",

@@ -14,6 +14,7 @@
 #include "../../compat.h"
 #include "../../functional.h"
 #include "default_srgemm_configuration.h"
+#include "user_functor_srgemm.h"
 
 namespace cuasr {
 namespace gemm {
@@ -31,6 +32,36 @@ inline cuasr_b200_scalar_t scalar(T v) {
   std::memcpy(s.bytes, &v, sizeof v);
   return s;
 }
+template <typename T>
+inline T unscalar(cuasr_b200_scalar_t const& s) {
+  T v;
+  std::memcpy(&v, s.bytes, sizeof v);
+  return v;
+}
+
+// Launch of the caller-compiled kernel for functors without an operator code.  The primary template is what a
+// host-only translation unit, or an operator whose functors both declare their codes, sees: it never names the
+// kernel, so nothing is instantiated for it.
+template <bool kCompileKernel, typename AdditionOp, typename MultiplicationOp, typename T, typename LayoutA,
+          typename LayoutB, typename LayoutC>
+struct UserFunctorPath {
+  static constexpr bool kAvailable = false;
+  static int run(cuasr_b200_args_t const&, cudaStream_t) { return CUASR_STATUS_ERROR_NOT_SUPPORTED; }
+};
+#if defined(__CUDACC__)
+template <typename AdditionOp, typename MultiplicationOp, typename T, typename LayoutA, typename LayoutB,
+          typename LayoutC>
+struct UserFunctorPath<true, AdditionOp, MultiplicationOp, T, LayoutA, LayoutB, LayoutC> {
+  static constexpr bool kAvailable = true;
+  static int run(cuasr_b200_args_t const& a, cudaStream_t stream) {
+    return run_user_functor_srgemm<AdditionOp, MultiplicationOp, T>(
+        a.m, a.n, a.k, static_cast<const T*>(a.A), a.lda, LayoutCode<LayoutA>::value == CUASR_ROW_MAJOR,
+        static_cast<const T*>(a.B), a.ldb, LayoutCode<LayoutB>::value == CUASR_ROW_MAJOR, static_cast<const T*>(a.C),
+        a.ldc, static_cast<T*>(a.D), a.ldd, LayoutCode<LayoutC>::value == CUASR_ROW_MAJOR, unscalar<T>(a.alpha),
+        unscalar<T>(a.beta), stream);
+  }
+};
+#endif
 }  // namespace detail
 
 template <typename AdditionOp_, typename MultiplicationOp_, typename ElementA_, typename LayoutA_,
@@ -113,19 +144,22 @@ class Srgemm {
   static cutlass::Status can_implement(Arguments const& args) {
     cuasr_b200_desc_t d = desc();
     cuasr_b200_args_t a = pack(args, nullptr, 0, nullptr);
+    if (user_functors()) return user_can_implement(a, SplitKSerial);
     return static_cast<cutlass::Status>(cuasr_b200_srgemm_can_implement(&d, &a));
   }
 
   static size_t get_workspace_size(Arguments const& args) {
     cuasr_b200_desc_t d = desc();
     cuasr_b200_args_t a = pack(args, nullptr, 0, nullptr);
+    if (user_functors()) return 0;
     return cuasr_b200_srgemm_workspace_size(&d, &a);
   }
 
   cutlass::Status initialize(Arguments const& args, void* workspace = nullptr, cudaStream_t stream = nullptr) {
     cuasr_b200_desc_t d = desc();
     cuasr_b200_args_t a = pack(args, workspace, get_workspace_size(args), stream);
-    cutlass::Status st = static_cast<cutlass::Status>(cuasr_b200_srgemm_can_implement(&d, &a));
+    cutlass::Status st = user_functors() ? user_can_implement(a, SplitKSerial)
+                                         : static_cast<cutlass::Status>(cuasr_b200_srgemm_can_implement(&d, &a));
     if (st != cutlass::Status::kSuccess) return st;
     if (a.workspace_bytes > 0 && workspace == nullptr) return cutlass::Status::kErrorWorkspaceNull;
     args_ = a;
@@ -149,6 +183,7 @@ class Srgemm {
     if (!initialized_) return cutlass::Status::kErrorInternal;
     cuasr_b200_desc_t d = desc();
     args_.stream = stream;
+    if (user_functors()) return static_cast<cutlass::Status>(UserPath::run(args_, stream));
     return static_cast<cutlass::Status>(cuasr_b200_srgemm(&d, &args_));
   }
 
@@ -160,6 +195,21 @@ class Srgemm {
   }
 
  protected:
+  // A functor pair the library has no operator codes for runs in a kernel compiled here from the functors themselves
+  // (user_functor_srgemm.h); that needs a CUDA compiler, so elsewhere such a pair is refused as not supported.
+  using UserPath = detail::UserFunctorPath<!(HasOpCode<AdditionOp>::value && HasOpCode<MultiplicationOp>::value),
+                                           AdditionOp, MultiplicationOp, ElementC, LayoutA, LayoutB, LayoutC>;
+  static bool user_functors() {
+    return UserPath::kAvailable &&
+           (OpCodeOf<AdditionOp, ElementC>::get() < 0 || OpCodeOf<MultiplicationOp, ElementC>::get() < 0);
+  }
+  static cutlass::Status user_can_implement(cuasr_b200_args_t const& a, bool slices_allowed) {
+    if (a.m <= 0 || a.n <= 0 || a.k <= 0 || a.A == nullptr || a.B == nullptr || a.D == nullptr || a.split_k_slices < 1)
+      return cutlass::Status::kErrorInvalidProblem;
+    if (a.split_k_slices > 1 && !slices_allowed) return cutlass::Status::kErrorInvalidProblem;
+    return cutlass::Status::kSuccess;
+  }
+
   static cuasr_b200_desc_t desc() {
     cuasr_b200_desc_t d;
     d.add_op = OpCodeOf<AdditionOp, ElementC>::get();

@@ -63,19 +63,23 @@ class SrgemmSplitKParallel
   static cutlass::Status can_implement(Arguments const& args) {
     cuasr_b200_desc_t d = Base::desc();
     cuasr_b200_args_t a = Base::pack(args, nullptr, 0, nullptr);
+    if (Base::user_functors()) return Base::user_can_implement(a, true);
     return static_cast<cutlass::Status>(cuasr_b200_srgemm_splitk_can_implement(&d, &a));
   }
 
   static size_t get_workspace_size(Arguments const& args) {
     cuasr_b200_desc_t d = Base::desc();
     cuasr_b200_args_t a = Base::pack(args, nullptr, 0, nullptr);
+    if (Base::user_functors()) return 0;    // the caller-compiled kernel contracts all of K in one pass
     return cuasr_b200_srgemm_splitk_workspace_size(&d, &a);
   }
 
   cutlass::Status initialize(Arguments const& args, void* workspace, cudaStream_t stream = nullptr) {
     cuasr_b200_desc_t d = Base::desc();
     cuasr_b200_args_t a = Base::pack(args, workspace, get_workspace_size(args), stream);
-    cutlass::Status st = static_cast<cutlass::Status>(cuasr_b200_srgemm_splitk_can_implement(&d, &a));
+    cutlass::Status st = Base::user_functors()
+                             ? Base::user_can_implement(a, true)
+                             : static_cast<cutlass::Status>(cuasr_b200_srgemm_splitk_can_implement(&d, &a));
     if (st != cutlass::Status::kSuccess) return st;
     if (a.workspace_bytes > 0 && workspace == nullptr) return cutlass::Status::kErrorWorkspaceNull;
     this->args_ = a;
@@ -89,6 +93,7 @@ class SrgemmSplitKParallel
     if (!this->initialized_) return cutlass::Status::kErrorInternal;
     cuasr_b200_desc_t d = Base::desc();
     this->args_.stream = stream;
+    if (Base::user_functors()) return static_cast<cutlass::Status>(Base::UserPath::run(this->args_, stream));
     return static_cast<cutlass::Status>(cuasr_b200_srgemm_splitk(&d, &this->args_));
   }
 

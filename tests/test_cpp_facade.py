@@ -47,6 +47,9 @@ template <typename T> struct my_mul  { T operator()(T l, T const& r) const { ret
 template <typename T> struct my_land { T operator()(T l, T const& r) const { return T(l && r); } };
 template <typename T> struct my_lor  { T operator()(T l, T const& r) const { return T(l || r); } };
 template <typename T> struct my_sub  { T operator()(T l, T const& r) const { return l - r; } };
+// agree with plus / multiplies on small values only: must NOT be taken for them
+template <typename T> struct my_satadd { T operator()(T l, T const& r) const { T s = l + r; return s < T(100) ? s : T(100); } };
+template <typename T> struct my_modmul { T operator()(T l, T const& r) const { return T((long long)(l * r) % 1000003); } };
 struct tagged { static constexpr int kOpCode = CUASR_OP_MAXIMUM; float operator()(float l, float const& r) const { return l - r; } };
 int main() {
   int bad = 0;
@@ -55,6 +58,7 @@ int main() {
   EXPECT(my_min, float, CUASR_OP_MINIMUM) EXPECT(my_max, double, CUASR_OP_MAXIMUM)     EXPECT(my_add, float, CUASR_OP_PLUS)
   EXPECT(my_mul, double, CUASR_OP_MULTIPLIES) EXPECT(my_land, int, CUASR_OP_BINARY_AND) EXPECT(my_lor, float, CUASR_OP_BINARY_OR)
   EXPECT(my_min, int, CUASR_OP_MINIMUM)   EXPECT(my_sub, float, -1)                    EXPECT(my_sub, int, -1)
+  EXPECT(my_satadd, float, -1)            EXPECT(my_satadd, int, -1)                   EXPECT(my_modmul, int, -1)
   EXPECT(cuasr::minimum, float, CUASR_OP_MINIMUM)                                      // declared functors are not probed
   if (cuasr::OpCodeOf<tagged, float>::get() != CUASR_OP_MAXIMUM) ++bad;               // kOpCode wins over behaviour
   return bad;
@@ -69,6 +73,18 @@ def test_undeclared_functors_are_recognised_by_what_they_compute(tmp_path):
                     str(src), "-o", str(exe)], check=True)
     res = subprocess.run([str(exe)], capture_output=True, text=True)
     assert res.returncode == 0, res.stdout
+
+
+@pytest.mark.gpu
+def test_user_defined_functors_run_as_compiled_kernels(cuda_device):
+    """Functors without an operator code (a saturating sum, a non-commutative product) through the drop-in templates:
+    the headers compile them into a kernel in the caller's translation unit, as the reference does with every functor;
+    the program checks the reference's ragged grid in all eight layouts against host loops over the same functors."""
+    binary = os.path.join(ROOT, "tests", "cpp", "user_functors")
+    assert os.path.exists(binary), "build it with __graft_entry__.build()"
+    res = subprocess.run([binary], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "ALL OK" in res.stdout
 
 
 @pytest.mark.gpu
