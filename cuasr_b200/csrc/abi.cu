@@ -201,10 +201,53 @@ size_t ticket_bytes_for(const cuasr_b200_args_t& args) { return align_up(tile_co
 // Scratch layout: [tickets: one u32 per 128 x 128 tile, padded to 256 B][partials: one full 128 x 128 block per
 // (split tile, slice)].  With every tile split (explicit split-K) that is tiles * slices blocks, which also
 // covers the slices * m * n elements the fallback kernel needs.
+size_t splitk_bytes_for_pieces(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, long long pieces) {
+  const size_t es = desc.dtype == CUASR_F64 ? 8 : 4;
+  return ticket_bytes_for(args) + es * tile_count(args) * kTileM * kTileN * static_cast<size_t>(pieces);
+}
+
+// Explicit split-K: how many pieces each caller slice is cut into.  The reference launches exactly tiles x slices
+// CTAs (include/cuasr/gemm/kernel/srgemm_splitk_parallel.h:86-89), whatever the GPU; here a slice count that leaves
+// SMs idle (4 tiles x 16 slices = 64 work items on 148 SMs) is refined: every slice is cut into `sub` pieces of
+// consecutive K tiles, so the fold order stays slice-major, piece-minor.  That is only done where (+) is exact and
+// order-independent (everything but floating-point plus), so the result cannot depend on the SM count.  The cost
+// model counts K tiles: waves x (K tiles per piece) for the contraction, plus half a K tile per piece for parking
+// and folding a 128 x 128 partial.
+bool splitk_order_independent(const cuasr_b200_desc_t& desc) {
+  return !(desc.add_op == CUASR_OP_PLUS && (desc.dtype == CUASR_F32 || desc.dtype == CUASR_F64));
+}
+int splitk_sub_pieces(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int sms) {
+  if (sms <= 0 || args.split_k_slices <= 1 || !splitk_order_independent(desc)) return 1;
+  const int tk = kTileKBytes / (desc.dtype == CUASR_F64 ? 8 : 4);
+  const long long k_tiles = (args.k + tk - 1) / tk;
+  const long long tiles = static_cast<long long>(tile_count(args));
+  auto cost = [&](long long pieces) {
+    const long long waves = (tiles * pieces + sms - 1) / sms;
+    return static_cast<double>(waves * ((k_tiles + pieces - 1) / pieces)) + 0.5 * static_cast<double>(pieces);
+  };
+  int best = 1;
+  double best_cost = cost(args.split_k_slices);
+  for (int sub = 2; sub <= 8; ++sub) {
+    const long long pieces = static_cast<long long>(args.split_k_slices) * sub;
+    if (pieces * 4 > k_tiles) break;                      // keep at least four K tiles per piece
+    const double c = cost(pieces);
+    if (c < 0.95 * best_cost) { best = sub; best_cost = c; }
+  }
+  return best;
+}
+
+// Workspace the split-K entry points ask for: room for the refined plan on the current GPU (the plain
+// tiles x slices layout where no GPU is visible).  A smaller workspace, down to the plain layout, is accepted at run
+// time and simply limits the refinement.
 size_t splitk_workspace_bytes(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args) {
   if (args.split_k_slices <= 1) return 0;
-  const size_t es = desc.dtype == CUASR_F64 ? 8 : 4;
-  return ticket_bytes_for(args) + es * tile_count(args) * kTileM * kTileN * args.split_k_slices;
+  return splitk_bytes_for_pieces(desc, args, args.split_k_slices);
+}
+size_t splitk_workspace_bytes_refined(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args) {
+  if (args.split_k_slices <= 1) return 0;
+  DeviceState* dev = nullptr;
+  const int sub = device_state(&dev) ? splitk_sub_pieces(desc, args, dev->sms) : 1;
+  return splitk_bytes_for_pieces(desc, args, static_cast<long long>(args.split_k_slices) * sub);
 }
 
 // Load balancing of a launch that was not asked to split K: the tiles of the last, partial wave are cut along K
@@ -305,7 +348,9 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
     if (args.workspace == nullptr) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
     if (args.workspace_bytes < need) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
     if (!workspace_aligned) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
-    plan = BalancePlan{0, slices};
+    int sub = splitk_sub_pieces(desc, args, dev->sms);
+    while (sub > 1 && args.workspace_bytes < splitk_bytes_for_pieces(desc, args, static_cast<long long>(slices) * sub)) --sub;
+    plan = BalancePlan{0, slices * sub};
   } else if (args.workspace != nullptr && workspace_aligned) {
     // an optional workspace on an unsplit launch buys load balancing, if it is large enough for the plan
     constexpr int tk = kTileKBytes / sizeof(T);
@@ -540,7 +585,7 @@ int cuasr_b200_srgemm_can_implement(const cuasr_b200_desc_t* desc, const cuasr_b
 
 size_t cuasr_b200_srgemm_workspace_size(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
   if (desc == nullptr || args == nullptr) return 0;
-  if (desc->split_k_serial && args->split_k_slices > 1) return splitk_workspace_bytes(*desc, *args);
+  if (desc->split_k_serial && args->split_k_slices > 1) return splitk_workspace_bytes_refined(*desc, *args);
   return 0;
 }
 
@@ -583,7 +628,7 @@ int cuasr_b200_srgemm_splitk_can_implement(const cuasr_b200_desc_t* desc, const 
 
 size_t cuasr_b200_srgemm_splitk_workspace_size(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {
   if (desc == nullptr || args == nullptr) return 0;
-  return splitk_workspace_bytes(*desc, *args);
+  return splitk_workspace_bytes_refined(*desc, *args);
 }
 
 int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t* desc, const cuasr_b200_args_t* args) {

@@ -208,6 +208,25 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
   T acc[8][8];
 
+  // Per-lane byte offsets of the eight 16-byte k chunks of a K-contiguous operand row, swizzle applied: computed
+  // once, so that inside the contraction an operand vector is addressed as (stage base + one of these + a constant).
+  // Only for 4-byte elements: with 8-byte elements the accumulators leave no registers for the table, and the
+  // offsets are computed where they are used.
+  constexpr bool kOffsetTable = sizeof(T) == 4;
+  // chunks unrolled in the contraction loop; the table holds the offsets of that many chunks, and chunk c + kUnroll
+  // of a stage is reached by flipping bit 6 of the offset (bit 2 of the chunk index; a_base and b_base are
+  // multiples of 128, so the flip commutes with adding them)
+  // (four chunks keep the loop body near 16 KiB of instructions; unrolling all eight measured the same on min-plus
+  // and 25 % slower on max-min, whose body is half as large again)
+  constexpr int kUnroll = 4;
+  uint32_t a_off[kOffsetTable ? kUnroll : 1], b_off[kOffsetTable ? 8 : 1];
+  if constexpr (kOffsetTable) {
+#pragma unroll
+    for (int c = 0; c < kUnroll; ++c) a_off[c] = a_base + (((c ^ lr) & 7) << 4);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) b_off[c] = b_base + (((c ^ lc) & 7) << 4);      // rows lc + 4 j with odd j use b_off[c ^ 4]
+  }
+
   uint32_t it = 0;
   for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
     int tile, z, pieces, tm, tn;
@@ -227,10 +246,14 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       const uint32_t sa = smem_base + s * kStageBytes;
       const uint32_t sb = sa + kOperandStageBytes;
 
-      // fragment loaders for one 16-byte k chunk: a[i][e] = A(row i, k = chunk * EV + e)
-      auto load_a = [&](T (&a)[8][EV], int chunk) {
+      // fragment loaders for one 16-byte k chunk: a[i][e] = A(row i, k = chunk * EV + e).  With the offset table the
+      // chunk is given as (c, h): chunk = h * kUnroll + c with c a compile-time constant; without it h is 0.
+      auto load_a = [&](T (&a)[8][EV], int c, int h = 0) {
+        const int chunk = kOffsetTable ? h * kUnroll + c : c;
         if (kAK) {
-          const uint32_t base = sa + a_base + (((chunk ^ lr) & 7) << 4);
+          uint32_t base;
+          if constexpr (kOffsetTable) base = sa + (a_off[c] ^ (h << 6));
+          else base = sa + a_base + (((chunk ^ lr) & 7) << 4);
 #pragma unroll
           for (int i = 0; i < 8; ++i) lds16(base + i * 1024, a[i]);
         } else {
@@ -247,10 +270,17 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
         }
       };
-      auto load_b = [&](T (&b)[8][EV], int chunk) {
+      auto load_b = [&](T (&b)[8][EV], int c, int h = 0) {
+        const int chunk = kOffsetTable ? h * kUnroll + c : c;
         if (kBK) {
-          const uint32_t base0 = sb + b_base + (((chunk ^ lc) & 7) << 4);
-          const uint32_t base1 = sb + b_base + (((chunk ^ (lc + 4)) & 7) << 4);
+          uint32_t base0, base1;
+          if constexpr (kOffsetTable) {
+            base0 = sb + (b_off[c] ^ (h << 6));
+            base1 = sb + (b_off[c ^ 4] ^ (h << 6));
+          } else {
+            base0 = sb + b_base + (((chunk ^ lc) & 7) << 4);
+            base1 = sb + b_base + (((chunk ^ (lc + 4)) & 7) << 4);
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) lds16(((j & 1) ? base1 : base0) + j * 512, b[j]);
         } else {
@@ -358,18 +388,27 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       } else if constexpr (sizeof(T) == 4) {
         // 4-byte elements: operand fragments are double-buffered in registers (64 + 4 x 32 registers)
         T a0[8][EV], b0[8][EV], a1[8][EV], b1[8][EV];
-        load_a(a0, 0);
-        load_b(b0, 0);
+        load_a(a0, 0, 0);
+        load_b(b0, 0, 0);
+        // kUnroll chunks at a time with compile-time chunk indices, so that the only integer work left per chunk is
+        // combining the stage base with a table entry (integer instructions share the half-rate pipe with the
+        // three-input min: each one costs as much as a product pair)
 #pragma unroll 1
-        for (int chunk = 0; chunk < kChunks; chunk += 2) {
-          load_a(a1, chunk + 1);
-          load_b(b1, chunk + 1);
-          compute(a0, b0);
-          if (chunk + 2 < kChunks) {
-            load_a(a0, chunk + 2);
-            load_b(b0, chunk + 2);
+        for (int h = 0; h < kChunks / kUnroll; ++h) {
+#pragma unroll
+          for (int c = 0; c < kUnroll; c += 2) {
+            load_a(a1, c + 1, h);
+            load_b(b1, c + 1, h);
+            compute(a0, b0);
+            if (c + 2 < kUnroll) {
+              load_a(a0, c + 2, h);
+              load_b(b0, c + 2, h);
+            } else if (h + 1 < kChunks / kUnroll) {
+              load_a(a0, 0, h + 1);
+              load_b(b0, 0, h + 1);
+            }
+            compute(a1, b1);
           }
-          compute(a1, b1);
         }
       } else {
         // 8-byte elements: the 8 x 8 accumulators alone take 128 registers, so one fragment set is live

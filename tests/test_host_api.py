@@ -56,8 +56,10 @@ def test_workspace_sizes():
     need = par.get_workspace_size(a16)
     # at least what the reference asks for: sizeof(element) * M * N * slices (device/srgemm_splitk_parallel.h:226-235)
     assert need >= 4 * 256 * 256 * 16
-    assert need <= 4 * 256 * 256 * 16 + 4096
-    assert par.get_workspace_size(args(m=256, n=256, k=1 << 20, lda=1 << 20, ldb=1 << 20, slices=32)) > need
+    # no more than that where no GPU is visible; with a GPU each slice may be cut further to fill its SMs
+    gpu_visible = par._lib.cuasr_b200_device_status(None) >= 0
+    assert need <= (4 * 256 * 256 * 16 + 4096) * (8 if gpu_visible else 1)
+    assert par.get_workspace_size(args(m=256, n=256, k=1 << 20, lda=1 << 20, ldb=1 << 20, slices=32)) >= need
     f64 = SrgemmSplitKParallel(Op.MINIMUM, Op.PLUS, DType.F64, ROW, COL, ROW)
     assert f64.get_workspace_size(a16) >= 2 * (need - 4096)
     # ragged shapes are padded to whole 128 x 128 tiles
