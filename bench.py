@@ -315,6 +315,15 @@ def run_ours(args, wl):
     ldc = m if col_major_c else n
     A = wl.operand("A", dev)
     B = wl.operand("B", dev, c0 * k, cols * k) if world > 1 else wl.operand("B", dev)
+    if wl.ld_pad:
+        # same matrices, stored with padded leading dimensions
+        def padded(flat, ld):
+            lines = flat.numel() // ld
+            out = torch.zeros(lines * (ld + wl.ld_pad), dtype=flat.dtype, device=dev)
+            out.view(lines, ld + wl.ld_pad)[:, :ld].copy_(flat.view(lines, ld))
+            return out
+        A, B = padded(A, lda), padded(B, ldb)
+        lda, ldb = lda + wl.ld_pad, ldb + wl.ld_pad
     fill = float(ident) if tdt.is_floating_point else int(ident)
     C = torch.full((m * n,), fill, dtype=tdt, device=dev)
     push = world > 1 and args.exchange == "push"
@@ -336,7 +345,9 @@ def run_ours(args, wl):
     margs = Arguments((m, cols if world > 1 else n, k), (A, lda), (B, ldb), (C.data_ptr() + off, ldc),
                       (D.data_ptr() + off, ldc), (wl.alpha, wl.beta), wl.split_k_slices)
     ws = None
-    need = op.get_workspace_size(margs) or op.get_optional_workspace_size(margs)   # the second one is optional
+    need = op.get_workspace_size(margs)
+    if not need and not args.no_workspace:
+        need = op.get_optional_workspace_size(margs)            # never required: balanced last wave, re-packed operands
     if need:
         ws = torch.empty(need, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream()
@@ -403,7 +414,7 @@ def run_ours(args, wl):
     # layouts it cannot chunk fall back to copy, run, copy)
     from cuasr_b200 import HostSrgemm
     pipe = None
-    if wl.split_k_slices == 1:
+    if wl.split_k_slices == 1 and not wl.ld_pad:
         extra_fn = (lambda j, byte_off: [p + off + byte_off for r, p in enumerate(peer_d) if r != rank]) if push else None
         pipe = HostSrgemm(op, m, cols if world > 1 else n, k, wl.alpha, wl.beta, dev,
                           chunks=8 if world == 1 else max(1, min(8, cols // 512)),
@@ -825,6 +836,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="minplus_f32_8192")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--no-workspace", action="store_true",
+                    help="do not hand the library the optional workspace (no balanced last wave, no re-packed operands)")
     ap.add_argument("--no-apsp", action="store_true",
                     help="skip the n = 16384 APSP solve appended to the default workload's line (profiling runs)")
     ap.add_argument("--fw-block", type=int, default=0,

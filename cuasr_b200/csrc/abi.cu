@@ -317,10 +317,63 @@ bool repack_pays(const cuasr_b200_desc_t& desc, const Normalised& p) {
   const bool small_copy = rows * p.k < 4LL * 1024 * 1024;
   return small_copy || static_cast<long long>(p.m) * p.n >= 2048LL * rows;
 }
-size_t repack_operand_bytes(int rows, int k) { return align_up(static_cast<size_t>(rows) * align_up(k, 4) * 4, 256); }
-size_t repack_bytes(const cuasr_b200_desc_t& desc, const Normalised& p) {
-  if (!repack_pays(desc, p)) return 0;
-  return (p.a_kcontig ? 0 : repack_operand_bytes(p.m, p.k)) + (p.b_kcontig ? 0 : repack_operand_bytes(p.n, p.k));
+// Which operands a launch copies into K-contiguous, 16-byte aligned scratch before the TMA kernel runs:
+//   * an operand TMA cannot describe (its address or its leading dimension is not a multiple of 16 bytes; the
+//     reference accepts alignment 1, include/cuasr/gemm/device/default_srgemm_configuration.h:88-89) - otherwise the
+//     whole product would fall back to the generic kernel;
+//   * an MN-contiguous fp32 operand of a ring with a packed-add variant, where that pays (repack_pays).
+// Rows are padded to a multiple of 16 bytes; the padding is never read (the tensor map ends at K).
+struct RepackPlan {
+  bool a = false, b = false;
+  int k_padded = 0;      // > 0: both copies are extended along K to this length (a multiple of the kernel's K step)
+  size_t bytes = 0;
+};
+bool tma_describable(const void* ptr, long long ld, size_t es) {
+  return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && (ld * static_cast<long long>(es)) % 16 == 0;
+}
+size_t repack_operand_bytes(int rows, int k, size_t es) {
+  return align_up(static_cast<size_t>(rows) * align_up(static_cast<size_t>(k), 16 / es) * es, 256);
+}
+// Rings whose ragged last K step the TMA kernel pads by itself: floating min/max rings (out-of-range elements are
+// filled with NaN, which min and max ignore) and rings where 0 (x) 0 is neutral (zero fill).
+bool ring_pads_itself(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args) {
+  const bool is_float = desc.dtype == CUASR_F32 || desc.dtype == CUASR_F64;
+  if (is_float && (desc.add_op == CUASR_OP_MINIMUM || desc.add_op == CUASR_OP_MAXIMUM)) return true;
+  if (desc.add_op == CUASR_OP_PLUS && desc.mul_op == CUASR_OP_MULTIPLIES) return true;
+  if ((desc.add_op == CUASR_OP_BIT_OR || desc.add_op == CUASR_OP_BIT_XOR) &&
+      (desc.mul_op == CUASR_OP_BINARY_AND || desc.mul_op == CUASR_OP_BIT_AND))
+    return true;
+  if (desc.add_op == CUASR_OP_BINARY_OR && desc.mul_op == CUASR_OP_BINARY_AND) {
+    // zero fill is neutral when the accumulator starts at 0 or 1
+    switch (desc.dtype) {
+      case CUASR_F32: { const float v = load_scalar<float>(args.add_identity); return v == 0.0f || v == 1.0f; }
+      case CUASR_F64: { const double v = load_scalar<double>(args.add_identity); return v == 0.0 || v == 1.0; }
+      default:        { const uint32_t v = load_scalar<uint32_t>(args.add_identity); return v == 0u || v == 1u; }
+    }
+  }
+  return false;
+}
+// Every other ring (the integer min/max rings) has no value TMA could fill in.  With the optional workspace both
+// operands are copied and their K range is extended to a whole number of K steps: A with the additive identity, B
+// with the multiplicative one, so that every padded product is the additive identity.
+RepackPlan repack_plan(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, const Normalised& p) {
+  RepackPlan plan;
+  const size_t es = desc.dtype == CUASR_F64 ? 8 : 4;
+  // only problems the TMA kernel would take: not tiny, storage lines that do not overlap
+  if (static_cast<long long>(p.m) * p.n < 64 * 64) return plan;
+  if (p.lda < (p.a_kcontig ? p.k : p.m) || p.ldb < (p.b_kcontig ? p.k : p.n)) return plan;
+  const int tk = kTileKBytes / static_cast<int>(es);
+  if (p.k % tk != 0 && !ring_pads_itself(desc, args)) {
+    plan.a = plan.b = true;
+    plan.k_padded = (p.k + tk - 1) / tk * tk;
+  } else {
+    const bool pays = repack_pays(desc, p);
+    plan.a = !tma_describable(p.a, p.lda, es) || (pays && !p.a_kcontig);
+    plan.b = !tma_describable(p.b, p.ldb, es) || (pays && !p.b_kcontig);
+  }
+  const int k_copy = plan.k_padded > 0 ? plan.k_padded : p.k;
+  plan.bytes = (plan.a ? repack_operand_bytes(p.m, k_copy, es) : 0) + (plan.b ? repack_operand_bytes(p.n, k_copy, es) : 0);
+  return plan;
 }
 
 template <typename T>
@@ -357,32 +410,34 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
     const BalancePlan wish = balance_plan(static_cast<long long>(tile_count(args)), dev->sms, (args.k + tk - 1) / tk);
     if (wish.pieces > 1 && args.workspace_bytes >= balance_workspace_bytes(desc, args, dev->sms)) plan = wish;
   }
-  // the rest of an optional workspace holds K-contiguous copies of MN-contiguous fp32 operands
+  // the rest of an optional workspace holds K-contiguous, aligned copies of operands (see RepackPlan)
   bool repacked = false;
-  if constexpr (std::is_same<T, float>::value) {
-    if (slices == 1 && args.workspace != nullptr && workspace_aligned) {
-      const size_t first = align_up(balance_workspace_bytes(desc, args, dev->sms), 256);
-      const size_t extra_bytes = repack_bytes(desc, p);
-      if (extra_bytes > 0 && args.workspace_bytes >= first + extra_bytes) {
-        char* cursor = static_cast<char*>(args.workspace) + first;
-        const long long ldt = static_cast<long long>(align_up(p.k, 4));
-        if (!p.a_kcontig) {
-          if (launch_transpose_f32(static_cast<const float*>(p.a), p.lda, p.m, p.k, reinterpret_cast<float*>(cursor),
-                                   ldt, stream) != cudaSuccess)
-            return CUASR_STATUS_ERROR_INTERNAL;
-          g_launches.fetch_add(1);
-          p.a = cursor; p.lda = ldt; p.a_kcontig = true;
-          cursor += repack_operand_bytes(p.m, p.k);
-        }
-        if (!p.b_kcontig) {
-          if (launch_transpose_f32(static_cast<const float*>(p.b), p.ldb, p.n, p.k, reinterpret_cast<float*>(cursor),
-                                   ldt, stream) != cudaSuccess)
-            return CUASR_STATUS_ERROR_INTERNAL;
-          g_launches.fetch_add(1);
-          p.b = cursor; p.ldb = ldt; p.b_kcontig = true;
-        }
-        repacked = true;
+  int k_map = p.k;              // K extent the tensor maps describe
+  if (slices == 1 && args.workspace != nullptr && workspace_aligned) {
+    const size_t first = align_up(balance_workspace_bytes(desc, args, dev->sms), 256);
+    const RepackPlan rp = repack_plan(desc, args, p);
+    if (rp.bytes > 0 && args.workspace_bytes >= first + rp.bytes) {
+      char* cursor = static_cast<char*>(args.workspace) + first;
+      const int k_copy = rp.k_padded > 0 ? rp.k_padded : p.k;
+      const long long ldt = static_cast<long long>(align_up(static_cast<size_t>(k_copy), 16 / sizeof(T)));
+      unsigned long long pad_a = 0, pad_b = 0;
+      std::memcpy(&pad_a, &add_id, sizeof(T));
+      std::memcpy(&pad_b, &mul_id, sizeof(T));
+      if (rp.a) {
+        if (launch_repack(p.a, p.lda, p.a_kcontig, p.m, p.k, k_copy, pad_a, cursor, ldt, sizeof(T), stream) != cudaSuccess)
+          return CUASR_STATUS_ERROR_INTERNAL;
+        g_launches.fetch_add(1);
+        p.a = cursor; p.lda = ldt; p.a_kcontig = true;
+        cursor += repack_operand_bytes(p.m, k_copy, sizeof(T));
       }
+      if (rp.b) {
+        if (launch_repack(p.b, p.ldb, p.b_kcontig, p.n, p.k, k_copy, pad_b, cursor, ldt, sizeof(T), stream) != cudaSuccess)
+          return CUASR_STATUS_ERROR_INTERNAL;
+        g_launches.fetch_add(1);
+        p.b = cursor; p.ldb = ldt; p.b_kcontig = true;
+      }
+      repacked = true;
+      k_map = k_copy;
     }
   }
   if (plan.pieces > 1) {
@@ -402,7 +457,7 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
        (desc.mul_op == CUASR_OP_BINARY_AND || desc.mul_op == CUASR_OP_BIT_AND)) ||
       (desc.add_op == CUASR_OP_BINARY_OR && desc.mul_op == CUASR_OP_BINARY_AND && (add_id == T(0) || add_id == T(1)));
   const bool nan_pad = is_float && min_or_max;
-  const bool paddable = nan_pad || zero_pad_ok || (p.k % TK == 0);
+  const bool paddable = nan_pad || zero_pad_ok || (k_map % TK == 0);
   auto tma_ok = [&](const void* ptr, long long ld) {
     return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && (ld * (long long)sizeof(T)) % 16 == 0;
   };
@@ -415,8 +470,8 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
   bool launched = false;
   if (use_tma) {
     CUtensorMap map_a, map_b;
-    if (make_operand_map<T>(&map_a, static_cast<const T*>(p.a), p.lda, p.m, p.k, p.a_kcontig, nan_pad) &&
-        make_operand_map<T>(&map_b, static_cast<const T*>(p.b), p.ldb, p.n, p.k, p.b_kcontig, nan_pad)) {
+    if (make_operand_map<T>(&map_a, static_cast<const T*>(p.a), p.lda, p.m, k_map, p.a_kcontig, nan_pad) &&
+        make_operand_map<T>(&map_b, static_cast<const T*>(p.b), p.ldb, p.n, k_map, p.b_kcontig, nan_pad)) {
       TmaParams<T> tp;
       tp.M = p.m; tp.N = p.n; tp.K = p.k;
       tp.C = static_cast<const T*>(p.c); tp.ldc = p.ldc;
@@ -594,7 +649,7 @@ size_t cuasr_b200_srgemm_optional_workspace_size(const cuasr_b200_desc_t* desc, 
   if (args->split_k_slices > 1) return 0;
   DeviceState* dev = nullptr;
   if (!device_state(&dev)) return 0;
-  const size_t repack = repack_bytes(*desc, normalise(*desc, *args));
+  const size_t repack = repack_plan(*desc, *args, normalise(*desc, *args)).bytes;
   const size_t balance = balance_workspace_bytes(*desc, *args, dev->sms);
   return repack > 0 ? align_up(balance, 256) + repack : balance;
 }

@@ -120,25 +120,31 @@ splitk_reduce_kernel(GenericParams<typename RingT::Element> p, int slices) {
   for (int x = 0; x < p.n_extra; ++x) p.extra_d[x][(long long)m * p.ldd + n] = v;
 }
 
-// Re-packs an MN-contiguous operand (element (r, k) at src[r + k * ld_src]) into K-contiguous storage
-// (dst[r * ld_dst + k]) through 32 x 32 shared-memory tiles; reads and writes are both coalesced.
-template <typename T>
+// Re-packs a rows x K operand into K-contiguous storage (dst[r * ld_dst + k]) through 32 x 32 shared-memory tiles.
+// The source is either MN-contiguous (element (r, k) at src[r + k * ld_src]: a transposition, reads and writes both
+// coalesced) or K-contiguous with a leading dimension or address TMA cannot use (src[r * ld_src + k]: a copy).
+// W is an unsigned integer of the element's width: the data is only moved.  Tiles are numbered along grid.x
+// (rows fastest), so neither extent is limited by the 65535 of the other grid dimensions.
+template <typename W>
 __global__ void __launch_bounds__(256)
-transpose_to_kcontig_kernel(const T* __restrict__ src, long long ld_src, int rows, int K, T* __restrict__ dst,
-                            long long ld_dst) {
-  __shared__ T tile[32][33];
-  const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+repack_to_kcontig_kernel(const W* __restrict__ src, long long ld_src, int src_kcontig, int rows, int K, int K_out,
+                         W pad, W* __restrict__ dst, long long ld_dst, int tiles_r) {
+  __shared__ W tile[32][33];
+  const int r0 = (blockIdx.x % tiles_r) * 32, k0 = (blockIdx.x / tiles_r) * 32;
   const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;   // 32 x 8
+  if (!src_kcontig) {
 #pragma unroll
-  for (int i = 0; i < 32; i += 8) {
-    const int r = r0 + tx, k = k0 + ty + i;
-    if (r < rows && k < K) tile[ty + i][tx] = src[r + (long long)k * ld_src];
+    for (int i = 0; i < 32; i += 8) {
+      const int r = r0 + tx, k = k0 + ty + i;
+      if (r < rows && k < K) tile[ty + i][tx] = src[r + (long long)k * ld_src];
+    }
+    __syncthreads();
   }
-  __syncthreads();
 #pragma unroll
   for (int i = 0; i < 32; i += 8) {
     const int r = r0 + ty + i, k = k0 + tx;
-    if (r < rows && k < K) dst[(long long)r * ld_dst + k] = tile[tx][ty + i];
+    if (r < rows && k < K_out)
+      dst[(long long)r * ld_dst + k] = k >= K ? pad : src_kcontig ? src[(long long)r * ld_src + k] : tile[tx][ty + i];
   }
 }
 

@@ -42,8 +42,11 @@ cudaError_t launch_generic(const GenericParams<T>& params, int slices, cudaStrea
 template <int ADD, int MUL, typename T>
 cudaError_t launch_generic_reduce(const GenericParams<T>& params, int slices, cudaStream_t stream);
 
-// Copies an MN-contiguous rows x K operand into K-contiguous storage (see transpose_to_kcontig_kernel).
-cudaError_t launch_transpose_f32(const float* src, long long ld_src, int rows, int K, float* dst, long long ld_dst,
-                                 cudaStream_t stream);
+// Copies a rows x K operand of 4- or 8-byte elements, K-contiguous or MN-contiguous with any leading dimension and
+// alignment, into K-contiguous storage with leading dimension ld_dst; columns K .. K_out - 1 of the copy are set to
+// the element whose bits are `pad_bits` (see repack_to_kcontig_kernel).
+cudaError_t launch_repack(const void* src, long long ld_src, bool src_kcontig, int rows, int K, int K_out,
+                          unsigned long long pad_bits, void* dst, long long ld_dst, size_t element_bytes,
+                          cudaStream_t stream);
 
 }  // namespace cuasr_b200

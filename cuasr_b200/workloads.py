@@ -38,6 +38,8 @@ class Workload:
     beta: float = 0.0
     split_k_slices: int = 1
     description: str = ""
+    ld_pad: int = 0                # elements added to the leading dimensions of A and B (an odd value makes them
+                                   # operands TMA cannot describe)
 
     @property
     def ops(self) -> float:
@@ -81,6 +83,9 @@ WORKLOADS = {w.name: w for w in [
     Workload("minplus_f32_8192", "minimum_plus", DType.F32, 8192, 8192, 8192, (COL, COL, COL), "uniform", 0.0, 100.0,
              description="north star: min-plus fp32, M = N = K = 8192, column-major, A, B uniform [0, 100), C = additive identity"),
     Workload("minplus_f32_4096", "minimum_plus", DType.F32, 4096, 4096, 4096, (COL, COL, COL), "uniform", 0.0, 100.0),
+    Workload("minplus_f32_4096_ld4097", "minimum_plus", DType.F32, 4096, 4096, 4096, (COL, COL, COL), "uniform", 0.0, 100.0,
+             ld_pad=1, description="min-plus fp32 4096^3 with leading dimension 4097 for A and B: operands TMA cannot "
+                                   "describe (the reference accepts any leading dimension)"),
     Workload("minplus_f32_512", "minimum_plus", DType.F32, 512, 512, 512, (COL, COL, COL), "uniform", 0.0, 100.0,
              description="config 1: the reference's own CPU-runnable case"),
     Workload("minplus_f64_8192", "minimum_plus", DType.F64, 8192, 8192, 8192, (COL, COL, COL), "graph", 1.0, 1000.0,

@@ -231,6 +231,88 @@ def test_balanced_launch_with_optional_workspace(cuda_device, ring, dt):
     assert device_status() == 0
 
 
+@pytest.mark.parametrize("ring,dt", [("minimum_plus", DType.F32), ("maximum_plus", DType.F64),
+                                     ("plus_multiplies", DType.F64), ("bit_xor_bit_and", DType.U32)])
+def test_unaligned_operands_stay_on_the_tma_kernel_with_the_workspace(cuda_device, ring, dt):
+    """The reference accepts any leading dimension and element-aligned pointers
+    (include/cuasr/gemm/device/default_srgemm_configuration.h:88-89, test/device/testbed.h:313-319).  TMA cannot
+    describe an operand whose address or leading dimension is not a multiple of 16 bytes: without a workspace such
+    a product runs on the generic kernel, with the optional workspace the operand is first copied into aligned
+    scratch and the fast kernel runs.  Either way the result is the host SRGEMM's."""
+    import torch
+    rng = np.random.default_rng(97)
+    m, n, k = 300, 260, 190
+    for layouts in util.ALL_LAYOUTS:
+        # odd leading dimensions for A and B, and views that start one element into their buffers
+        A, lda = util.make_matrix(rng, dt, layouts[0], m, k, ld=util.extents(layouts[0], m, k)[0] + 5)
+        B, ldb = util.make_matrix(rng, dt, layouts[1], k, n, ld=util.extents(layouts[1], k, n)[0] + 3)
+        C, ldc = util.make_matrix(rng, dt, layouts[2], m, n)
+        A, B = np.concatenate([A[:1], A]), np.concatenate([B[:1], B])
+        alpha, _ = util.default_scalars(ring, dt)
+        want = util.run_oracle(ring, dt, layouts, (m, n, k), alpha, A[1:].copy(), lda, B[1:].copy(), ldb, alpha, C, ldc)
+
+        def dev(x):
+            return torch.from_numpy(x.view(np.int32) if x.dtype == np.uint32 else x).cuda()
+        dA, dB, dC = dev(A), dev(B), dev(C)
+        dD = torch.zeros_like(dC)
+        es = dA.element_size()
+        op = Srgemm(*RINGS[ring], dt, *layouts)
+        args = Arguments((m, n, k), (dA.data_ptr() + es, lda), (dB.data_ptr() + es, ldb), (dC, ldc), (dD, ldc),
+                         (alpha, alpha))
+        assert op(args) == Status.kSuccess
+        torch.cuda.synchronize()
+        assert op.last_kernel() == "generic"
+        got = dD.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32) if dt == DType.U32 else got, want), (ring, layouts, "generic")
+        need = op.get_optional_workspace_size(args)
+        assert need > 0
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        dD.zero_()
+        assert op(args, ws) == Status.kSuccess
+        torch.cuda.synchronize()
+        assert op.last_kernel().startswith("tma"), op.last_kernel()
+        got = dD.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32) if dt == DType.U32 else got, want), (ring, layouts, "repacked")
+    assert device_status() == 0
+
+
+@pytest.mark.parametrize("ring,dt", [("minimum_plus", DType.S32), ("maximum_plus", DType.U32),
+                                     ("minimum_maximum", DType.S32), ("maximum_minimum", DType.U32)])
+def test_integer_rings_with_ragged_k_use_padded_copies(cuda_device, ring, dt):
+    """Integer min/max rings have no value TMA could fill a ragged last K step with.  With the optional workspace
+    both operands are copied with K extended to whole steps - A by the additive identity, B by the multiplicative
+    one - and the TMA kernel runs; without it the generic kernel does."""
+    import torch
+    rng = np.random.default_rng(5)
+    for layouts in (util.ALL_LAYOUTS[0], util.ALL_LAYOUTS[3], util.ALL_LAYOUTS[6]):
+        for (m, n, k) in ((256, 192, 100), (130, 300, 77)):
+            A, lda = util.make_matrix(rng, dt, layouts[0], m, k)
+            B, ldb = util.make_matrix(rng, dt, layouts[1], k, n)
+            C, ldc = util.make_matrix(rng, dt, layouts[2], m, n)
+            alpha, _ = util.default_scalars(ring, dt)
+            want = util.run_oracle(ring, dt, layouts, (m, n, k), alpha, A, lda, B, ldb, alpha, C, ldc)
+
+            def dev(x):
+                return torch.from_numpy(x.view(np.int32) if x.dtype == np.uint32 else x).cuda()
+            dA, dB, dC = dev(A), dev(B), dev(C)
+            dD = torch.zeros_like(dC)
+            op = Srgemm(*RINGS[ring], dt, *layouts)
+            args = Arguments((m, n, k), (dA, lda), (dB, ldb), (dC, ldc), (dD, ldc), (alpha, alpha))
+            assert op(args) == Status.kSuccess
+            torch.cuda.synchronize()
+            assert op.last_kernel() == "generic"
+            need = op.get_optional_workspace_size(args)
+            assert need > 0
+            ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+            dD.zero_()
+            assert op(args, ws) == Status.kSuccess
+            torch.cuda.synchronize()
+            assert op.last_kernel().startswith("tma"), (op.last_kernel(), ring, layouts, m, n, k)
+            got = dD.cpu().numpy()
+            assert np.array_equal(got.view(np.uint32) if dt == DType.U32 else got, want), (ring, layouts, m, n, k)
+    assert device_status() == 0
+
+
 @pytest.mark.parametrize("layouts", [(COL, COL, COL), (ROW, COL, ROW), (ROW, ROW, ROW), (COL, ROW, COL)])
 def test_host_buffer_pipeline_equals_one_shot(cuda_device, layouts):
     """HostSrgemm (pinned host operands, chunked and overlapped copies) gives exactly the one-shot result."""
