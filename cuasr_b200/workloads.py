@@ -91,6 +91,8 @@ WORKLOADS = {w.name: w for w in [
     Workload("minplus_f64_8192", "minimum_plus", DType.F64, 8192, 8192, 8192, (COL, COL, COL), "graph", 1.0, 1000.0,
              density=0.1, add_identity=math.inf,
              description="config 2: weighted adjacency matrices, 10 % present in [1, 1000), absent = +inf, diagonal 0"),
+    Workload("minplus_f64_4096", "minimum_plus", DType.F64, 4096, 4096, 4096, (COL, COL, COL), "graph", 1.0, 1000.0,
+             density=0.1, add_identity=math.inf, description="config 2 at half the size (profiling captures)"),
     Workload("maxplus_f64_8192", "maximum_plus", DType.F64, 8192, 8192, 8192, (COL, COL, COL), "graph", 1.0, 1000.0,
              density=0.1, add_identity=-math.inf,
              description="config 2: as above with absent = -inf"),
