@@ -398,37 +398,37 @@ def run_ours(args, wl):
     value = wl.ops / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the host-buffer call: pinned host operands in, D out, every step ----
-    # With several ranks every byte of A crosses a host link once per node: rank r brings the r-th part of A's
-    # storage from its pinned buffer and an NVLink all-gather completes A on every GPU.
-    a_part = A.numel() // world
-    a_mine = slice(rank * a_part, (rank + 1) * a_part)
-    hA = torch.empty(a_part, dtype=tdt).pin_memory(); hA.copy_(A[a_mine])
-    hB = torch.empty(B.numel(), dtype=tdt).pin_memory(); hB.copy_(B)
+    # HostSrgemm = the library's host-buffer call: chunked copies overlapped with the kernel (split-K workloads and
+    # layouts it cannot chunk fall back to copy, run, copy).  With several ranks every byte of A crosses a host link
+    # once per node: each rank holds 1/world of every K piece of A in pinned memory, and the pipeline completes the
+    # pieces on every GPU with all-gathers over NVLink while earlier pieces compute.
+    from cuasr_b200 import HostSrgemm
     share = m * cols
     Cs, Ds = C[c0 * m: c0 * m + share], D[c0 * m: c0 * m + share]
-    hC = torch.empty(share, dtype=tdt).pin_memory(); hC.fill_(fill)
-    hD = torch.empty(share, dtype=tdt).pin_memory()
-    e2e_steps = max(1, min(args.steps, 5))
-
-    # HostSrgemm = the library's host-buffer call: chunked copies overlapped with the kernel (split-K workloads and
-    # layouts it cannot chunk fall back to copy, run, copy)
-    from cuasr_b200 import HostSrgemm
     pipe = None
     if wl.split_k_slices == 1 and not wl.ld_pad:
         extra_fn = (lambda j, byte_off: [p + off + byte_off for r, p in enumerate(peer_d) if r != rank]) if push else None
         pipe = HostSrgemm(op, m, cols if world > 1 else n, k, wl.alpha, wl.beta, dev,
                           chunks=8 if world == 1 else max(1, min(8, cols // 512)),
-                          extra_outputs_per_chunk=extra_fn, buffers=(A, B, Cs, Ds), shared_on_device=world > 1)
-
-    def bring_a():
-        A[a_mine].copy_(hA, non_blocking=True)
-        if world > 1:
-            dist.all_gather_into_tensor(A, A[a_mine])
+                          extra_outputs_per_chunk=extra_fn, buffers=(A, B, Cs, Ds),
+                          group=dist.group.WORLD if world > 1 else None, rank=rank, world=world)
+    if pipe is not None and world > 1:
+        ranges = pipe.shared_share_layout()
+    else:
+        a_part = A.numel() // world
+        ranges = [(rank * a_part, (rank + 1) * a_part)]
+    hA = torch.empty(sum(b - a for a, b in ranges), dtype=tdt).pin_memory()
+    pos = 0
+    for a, b in ranges:
+        hA[pos:pos + b - a].copy_(A[a:b])
+        pos += b - a
+    hB = torch.empty(B.numel(), dtype=tdt).pin_memory(); hB.copy_(B)
+    hC = torch.empty(share, dtype=tdt).pin_memory(); hC.fill_(fill)
+    hD = torch.empty(share, dtype=tdt).pin_memory()
+    e2e_steps = max(1, min(args.steps, 5))
 
     def e2e_step():
         if pipe is not None:
-            if world > 1:
-                bring_a()
             pipe(hA, hB, hC, hD, stream)
             if world > 1:
                 if push:
@@ -436,7 +436,11 @@ def run_ours(args, wl):
                 else:
                     dist.all_gather_into_tensor(D, Ds)
             return
-        bring_a(); B.copy_(hB, non_blocking=True); Cs.copy_(hC, non_blocking=True)
+        a0, a1 = ranges[0]
+        A[a0:a1].copy_(hA, non_blocking=True)
+        if world > 1:
+            dist.all_gather_into_tensor(A, A[a0:a1])
+        B.copy_(hB, non_blocking=True); Cs.copy_(hC, non_blocking=True)
         if launch() != Status.kSuccess:
             raise RuntimeError("SRGEMM launch failed")
         gather()

@@ -14,6 +14,11 @@ storage lines (column-major A, or row-major B for a row-major D) it is sent in a
 chunk is computed piece by piece, `D <- (alpha (x) A_p (x)(+) B_p) (+) D`, each piece as soon as it has arrived;
 (x) distributes over (+), and every ring except floating-point plus-times is exact, so the bits do not change
 (plus-times on floats keeps the one-piece schedule).
+
+Several ranks that shard the output (each computes its own lines of D) all need the shared operand.  With `group`
+set, every rank brings only its 1/world share of each K piece over its own host link and an all-gather over NVLink
+completes the piece on every GPU, so each byte of the shared operand crosses a host link once per node and the
+first chunk still starts after the first piece.
 """
 from __future__ import annotations
 
@@ -29,9 +34,14 @@ def _address(ref) -> int:
 
 class HostSrgemm:
     def __init__(self, operator: Srgemm, m: int, n: int, k: int, alpha, beta, device, chunks: int = 8,
-                 extra_outputs_per_chunk=None, buffers=None, shared_on_device: bool = False):
+                 extra_outputs_per_chunk=None, buffers=None, shared_on_device: bool = False, group=None,
+                 rank: int = 0, world: int = 1):
         """shared_on_device: the operand every chunk needs (A for a column-major D) is already in its device buffer
-        when the call starts (for instance assembled from the ranks' pieces over NVLink); it is not copied here."""
+        when the call starts; it is not copied here.
+        group, rank, world: torch.distributed group whose ranks all need the same shared operand (m, n, k describe
+        THIS rank's product).  The host tensor passed for the shared operand then holds this rank's share only:
+        for each of the `k_pieces` K pieces in turn, the rank-th of `world` equal parts of that piece's storage
+        (`shared_share_layout` gives the element ranges)."""
         import torch
 
         self.torch = torch
@@ -64,10 +74,56 @@ class HostSrgemm:
         # K pieces of the shared operand for the first chunk (see the module docstring)
         shared_lines_are_k = (col_c and la == Layout.COLUMN_MAJOR) or (not col_c and lb == Layout.ROW_MAJOR)
         exact = not (operator.add_op == Op.PLUS and operator.dtype in (DType.F32, DType.F64))
+        # every piece applies alpha to its own partial result, which is only right where alpha (x) distributes over
+        # (+): with (x) = multiplies under min or max that needs alpha >= 0 (a negative factor swaps min and max)
+        if operator.mul_op == Op.MULTIPLIES and operator.add_op in (Op.MINIMUM, Op.MAXIMUM) and not (alpha >= 0):
+            exact = False
         self.k_pieces = 4 if (self.chunkable and shared_lines_are_k and exact and k % 4 == 0 and k >= 512) else 1
         self.shared_on_device = bool(shared_on_device)
         if self.shared_on_device:
             self.k_pieces = 1
+        self.group, self.rank, self.world = group, int(rank), int(world)
+        if self.world > 1:
+            shared_elems = (m * k) if col_c else (k * n)
+            if self.k_pieces > 1 and (shared_elems // self.k_pieces) % self.world:
+                self.k_pieces = 1
+            if shared_elems % (self.k_pieces * self.world):
+                raise ValueError("the shared operand does not divide into equal shares for the ranks")
+            self.s_comm = torch.cuda.Stream(device=device)
+
+    def shared_share_layout(self):
+        """Element ranges [(start, stop), ...] of the shared operand's flat storage that make up this rank's share,
+        in the order the share's host tensor holds them (one range per K piece)."""
+        shared_elems = (self.m * self.k) if self.col_c else (self.k * self.n)
+        piece = shared_elems // self.k_pieces
+        sub = piece // self.world
+        return [(p * piece + self.rank * sub, p * piece + (self.rank + 1) * sub) for p in range(self.k_pieces)]
+
+    def _bring_shared_piece(self, shared_dev, shared_host, p: int):
+        """Starts the transfer of K piece p of the shared operand and returns the event that marks its arrival on
+        this GPU: a plain copy, or (several ranks) the copy of this rank's share followed by an all-gather."""
+        torch = self.torch
+        shared_elems = shared_dev.numel()
+        piece = shared_elems // self.k_pieces
+        arrived = torch.cuda.Event()
+        if self.world == 1:
+            rng = slice(p * piece, (p + 1) * piece)
+            with torch.cuda.stream(self.s_in):
+                shared_dev[rng].copy_(shared_host[rng], non_blocking=True)
+                arrived.record(self.s_in)
+            return arrived
+        import torch.distributed as dist
+        sub = piece // self.world
+        mine = slice(p * piece + self.rank * sub, p * piece + (self.rank + 1) * sub)
+        copied = torch.cuda.Event()
+        with torch.cuda.stream(self.s_in):
+            shared_dev[mine].copy_(shared_host[p * sub:(p + 1) * sub], non_blocking=True)
+            copied.record(self.s_in)
+        with torch.cuda.stream(self.s_comm):
+            self.s_comm.wait_event(copied)
+            dist.all_gather_into_tensor(shared_dev[p * piece:(p + 1) * piece], shared_dev[mine], group=self.group)
+            arrived.record(self.s_comm)
+        return arrived
 
     def _chunk_args(self, j: int):
         """Arguments of chunk j and the element ranges of B (or A), C and D it touches."""
@@ -102,15 +158,9 @@ class HostSrgemm:
         """Chunk 0 as k_pieces accumulating launches, piece p as soon as K piece p of the shared operand is there."""
         torch = self.torch
         kp = self.k // self.k_pieces
-        line = self.m if self.col_c else self.n            # elements per K line of the shared operand
         (m, n, _), es = args.problem_size, self.es
         for p in range(self.k_pieces):
-            piece = slice(p * kp * line, (p + 1) * kp * line)
-            arrived = torch.cuda.Event()
-            with torch.cuda.stream(self.s_in):
-                shared_dev[piece].copy_(shared_host[piece], non_blocking=True)
-                arrived.record(self.s_in)
-            self.s_run.wait_event(arrived)
+            self.s_run.wait_event(self._bring_shared_piece(shared_dev, shared_host, p))
             if self.col_c:      # A column-major: K piece = columns of A; B chunk column-major: K piece = rows of B
                 a = (_address(args.ref_A[0]) + p * kp * self.lda * es, self.lda)
                 b = (_address(args.ref_B[0]) + p * kp * es, self.ldb)
@@ -142,9 +192,16 @@ class HostSrgemm:
                                        whole.ref_D, whole.epilogue)]
             need = max(self.op.get_optional_workspace_size(a) for a in shapes)
             self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=self.device)
+        whole_shared = None
         if self.k_pieces == 1 and not self.shared_on_device:
-            with torch.cuda.stream(self.s_in):
-                shared_dev.copy_(shared_host, non_blocking=True)
+            if self.world == 1:
+                with torch.cuda.stream(self.s_in):
+                    shared_dev.copy_(shared_host, non_blocking=True)
+            else:
+                self.s_comm.wait_event(start)
+                whole_shared = self._bring_shared_piece(shared_dev, shared_host, 0)
+        elif self.world > 1:
+            self.s_comm.wait_event(start)
         for j in range(self.chunks):
             args, moving, out = self._chunk_args(j)
             with torch.cuda.stream(self.s_in):
@@ -158,12 +215,14 @@ class HostSrgemm:
                 arrived = torch.cuda.Event()
                 arrived.record(self.s_in)
                 self.s_run.wait_event(arrived)
+                if whole_shared is not None:
+                    self.s_run.wait_event(whole_shared)
                 self._launch(args, extras, f"chunk {j}")
             done.record(self.s_run)
             self.s_out.wait_event(done)
             with torch.cuda.stream(self.s_out):
                 hD[out].copy_(self.dD[out], non_blocking=True)
-        for s in (self.s_run, self.s_out):
+        for s in (self.s_run, self.s_out) + ((self.s_comm,) if self.world > 1 else ()):
             end = torch.cuda.Event()
             end.record(s)
             cur.wait_event(end)

@@ -160,3 +160,66 @@ def test_multi_gpu_apsp(mode):
     want = cpu_apsp(random_graph(n, 0.01, seed, "cpu").numpy(), n, ShardedSquaring.squarings_needed(n))
     for rank in range(world):
         assert np.array_equal(out[(mode, rank)], want), f"{mode}: rank {rank} differs from the CPU solve"
+
+
+def _host_pipeline_rank(rank, world, port, m, n, k, out):
+    """One rank of a sharded host-buffer SRGEMM: its columns of D, its columns of B, its share of every K piece of A."""
+    import torch
+    import torch.distributed as dist
+    from cuasr_b200 import DType, HostSrgemm, Layout, RINGS, Srgemm, device_status
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    g = torch.Generator().manual_seed(1234)
+    A = torch.randint(-8, 9, (m * k,), generator=g).float()
+    B = torch.randint(-8, 9, (k * n,), generator=g).float()
+    C = torch.randint(-8, 9, (m * n,), generator=g).float()
+    cols = n // world
+    col = Layout.COLUMN_MAJOR
+    op = Srgemm(*RINGS["minimum_plus"], DType.F32, col, col, col)
+    pipe = HostSrgemm(op, m, cols, k, 0.0, 0.0, dev, chunks=2, group=dist.group.WORLD, rank=rank, world=world)
+    share = torch.cat([A[a:b] for a, b in pipe.shared_share_layout()]).pin_memory()
+    hB = B[rank * cols * k:(rank + 1) * cols * k].clone().pin_memory()
+    hC = C[rank * cols * m:(rank + 1) * cols * m].clone().pin_memory()
+    hD = torch.empty(cols * m, dtype=torch.float32).pin_memory()
+    for _ in range(2):
+        hD.zero_()
+        pipe(share, hB, hC, hD)
+        torch.cuda.synchronize()
+    out[("k_pieces", rank)] = pipe.k_pieces
+    out[("status", rank)] = device_status()
+    out[("D", rank)] = hD.numpy().copy()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_multi_gpu_host_buffer_pipeline():
+    """Ranks that shard the columns of D bring 1/world of every K piece of A each and complete the pieces with
+    all-gathers; the result is the one-shot host SRGEMM's, bit for bit."""
+    import torch
+    import torch.multiprocessing as mp
+    import oracle
+    from cuasr_b200 import DType, Layout, Op
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    m, n, k = 1024, 1024 * world, 1024
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = mp.Manager().dict()
+    mp.spawn(_host_pipeline_rank, args=(world, port, m, n, k, out), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(1234)
+    A = torch.randint(-8, 9, (m * k,), generator=g).float().numpy()
+    B = torch.randint(-8, 9, (k * n,), generator=g).float().numpy()
+    C = torch.randint(-8, 9, (m * n,), generator=g).float().numpy()
+    col = Layout.COLUMN_MAJOR
+    want = np.empty_like(C)
+    oracle.srgemm(Op.MINIMUM, Op.PLUS, DType.F32, (col, col, col), (m, n, k), 0.0, A, m, B, k, 0.0, C, m, want, m,
+                  np.finfo(np.float32).max)
+    cols = n // world
+    for rank in range(world):
+        assert out[("status", rank)] == 0
+        assert out[("k_pieces", rank)] == 4
+        assert np.array_equal(out[("D", rank)], want[rank * cols * m:(rank + 1) * cols * m]), f"rank {rank}"

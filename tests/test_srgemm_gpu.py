@@ -342,6 +342,31 @@ def test_host_buffer_pipeline_equals_one_shot(cuda_device, layouts):
     assert device_status() == 0
 
 
+def test_host_buffer_pipeline_with_a_negative_factor_under_min_times(cuda_device):
+    """alpha (x) min(x, y) is not min(alpha (x) x, alpha (x) y) when (x) is multiplication and alpha is negative, so
+    the first chunk must not be folded from K pieces that each apply alpha; the pipeline falls back to whole chunks
+    and still equals the host SRGEMM."""
+    import torch
+    from cuasr_b200 import HostSrgemm
+    rng = np.random.default_rng(78)
+    dt, ring, layouts = DType.F32, "minimum_multiplies", (COL, COL, COL)
+    m, n, k = 512, 512, 640
+    A, lda = util.make_matrix(rng, dt, layouts[0], m, k)
+    B, ldb = util.make_matrix(rng, dt, layouts[1], k, n)
+    C, ldc = util.make_matrix(rng, dt, layouts[2], m, n)
+    want = util.run_oracle(ring, dt, layouts, (m, n, k), -1.0, A, lda, B, ldb, 1.0, C, ldc)
+    op = Srgemm(*RINGS[ring], dt, *layouts)
+    pipe = HostSrgemm(op, m, n, k, -1.0, 1.0, cuda_device, chunks=4)
+    assert pipe.k_pieces == 1
+    assert HostSrgemm(op, m, n, k, 2.0, 1.0, cuda_device, chunks=4).k_pieces == 4
+    hA, hB, hC = (torch.from_numpy(x).pin_memory() for x in (A, B, C))
+    hD = torch.empty(m * n, dtype=torch.float32).pin_memory()
+    pipe(hA, hB, hC, hD)
+    torch.cuda.synchronize()
+    assert np.array_equal(hD.numpy(), want)
+    assert device_status() == 0
+
+
 def test_overlapping_operand_views(cuda_device):
     """A leading dimension shorter than the extent is an overlapping (sliding-window) view of a read-only operand;
     the reference accepts it (its examples/02 passes one) and so does this library, with the host SRGEMM's answer."""
