@@ -58,6 +58,18 @@ class ApspShardArgs(ctypes.Structure):     # cuasr_b200_apsp_shard_args_t
     ]
 
 
+class ApspMultiArgs(ctypes.Structure):     # cuasr_b200_apsp_multi_args_t
+    _fields_ = [
+        ("dtype", ctypes.c_int32), ("n", ctypes.c_int32), ("iterations", ctypes.c_int32), ("n_devices", ctypes.c_int32),
+        ("devices", ctypes.POINTER(ctypes.c_int32)),
+        ("buf0", ctypes.POINTER(ctypes.c_void_p)), ("buf1", ctypes.POINTER(ctypes.c_void_p)),
+        ("ldd", ctypes.c_int64),
+        ("workspace", ctypes.POINTER(ctypes.c_void_p)), ("workspace_bytes", ctypes.c_size_t),
+        ("streams", ctypes.POINTER(ctypes.c_void_p)),
+        ("result_buffer", ctypes.POINTER(ctypes.c_int32)), ("device_status", ctypes.POINTER(ctypes.c_int32)),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/*.h declares
 PROTOTYPES = {
     "cuasr_b200_srgemm_can_implement": (ctypes.c_int, [ctypes.POINTER(Desc), ctypes.POINTER(Args)]),
@@ -75,6 +87,9 @@ PROTOTYPES = {
     "cuasr_b200_apsp_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(ApspArgs)]),
     "cuasr_b200_apsp": (ctypes.c_int, [ctypes.POINTER(ApspArgs)]),
     "cuasr_b200_apsp_shard_squaring": (ctypes.c_int, [ctypes.POINTER(ApspShardArgs)]),
+    "cuasr_b200_apsp_multi": (ctypes.c_int, [ctypes.POINTER(ApspMultiArgs)]),
+    "cuasr_b200_apsp_multi_partition": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                                       ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
     "cuasr_b200_flag_raise": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_uint32,
                                              ctypes.c_void_p]),
     "cuasr_b200_flag_wait": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,

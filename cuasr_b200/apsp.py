@@ -428,3 +428,51 @@ def shard_squaring(dtype: DType, n: int, col0: int, cols: int, d_cur: int, ld_cu
     a.n_peers, a.peer_next = len(peer_next), ctypes.cast(peers, ctypes.POINTER(ctypes.c_void_p))
     a.workspace, a.workspace_bytes, a.stream = int(workspace) or None, int(workspace_bytes), int(stream) or None
     return Status(_lib.load().cuasr_b200_apsp_shard_squaring(ctypes.byref(a)))
+
+
+def multi_partition(n: int, n_devices: int, g: int):
+    """cuasr_b200_apsp_multi_partition: (first column, number of columns) of GPU g, or None for invalid arguments."""
+    import ctypes
+
+    from . import _lib
+
+    col0, cols = ctypes.c_int32(), ctypes.c_int32()
+    st = _lib.load().cuasr_b200_apsp_multi_partition(n, n_devices, g, ctypes.byref(col0), ctypes.byref(cols))
+    return (col0.value, cols.value) if st == 0 else None
+
+
+def multi_device_solve(dtype: DType, n: int, devices: Sequence[int], buf0: Sequence[int], buf1: Sequence[int],
+                       ldd: Optional[int] = None, iterations: int = 0, workspaces: Sequence[int] = (),
+                       workspace_bytes: int = 0, streams: Sequence[int] = ()):
+    """cuasr_b200_apsp_multi on device addresses: the sharded repeated-squaring solve on the GPUs `devices` of this
+    machine from one process (one host thread per GPU inside the library, peer stores between the GPUs).  buf0[g]
+    must hold the whole distance matrix on every GPU.  Returns (Status, index of the buffer that holds the result,
+    list of per-GPU device status words).  Blocks until the solve is done."""
+    import ctypes
+
+    from . import _lib
+
+    G = len(devices)
+    a = _lib.ApspMultiArgs()
+    a.dtype, a.n, a.iterations, a.n_devices = int(dtype), int(n), int(iterations), G
+    dev_arr = (ctypes.c_int32 * max(G, 1))(*[int(d) for d in devices])
+    b0 = (ctypes.c_void_p * max(G, 1))(*[int(p) or None for p in buf0])
+    b1 = (ctypes.c_void_p * max(G, 1))(*[int(p) or None for p in buf1])
+    a.devices = ctypes.cast(dev_arr, ctypes.POINTER(ctypes.c_int32))
+    a.buf0, a.buf1 = ctypes.cast(b0, ctypes.POINTER(ctypes.c_void_p)), ctypes.cast(b1, ctypes.POINTER(ctypes.c_void_p))
+    a.ldd = int(n if ldd is None else ldd)
+    keep = [dev_arr, b0, b1]
+    if workspaces:
+        ws = (ctypes.c_void_p * G)(*[int(p) or None for p in workspaces])
+        a.workspace, a.workspace_bytes = ctypes.cast(ws, ctypes.POINTER(ctypes.c_void_p)), int(workspace_bytes)
+        keep.append(ws)
+    if streams:
+        st_arr = (ctypes.c_void_p * G)(*[int(p) or None for p in streams])
+        a.streams = ctypes.cast(st_arr, ctypes.POINTER(ctypes.c_void_p))
+        keep.append(st_arr)
+    result = ctypes.c_int32(-1)
+    status = (ctypes.c_int32 * max(G, 1))()
+    a.result_buffer = ctypes.pointer(result)
+    a.device_status = ctypes.cast(status, ctypes.POINTER(ctypes.c_int32))
+    st = Status(_lib.load().cuasr_b200_apsp_multi(ctypes.byref(a)))
+    return st, result.value, list(status)[:G]

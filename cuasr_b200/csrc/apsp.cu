@@ -6,10 +6,15 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
+#include <condition_variable>
 #include <cstdint>
 #include <cstring>
 #include <limits>
+#include <mutex>
+#include <thread>
+#include <vector>
 
 #include "../../include/cuasr_b200_apsp.h"
 
@@ -231,6 +236,109 @@ int cuasr_b200_apsp_shard_squaring(const cuasr_b200_apsp_shard_args_t* a) {
     peers[p] = static_cast<char*>(a->peer_next[p]) + block_next;
   }
   return cuasr_b200_srgemm_push(&desc, &s, a->n_peers, peers);
+}
+
+int cuasr_b200_apsp_multi_partition(int32_t n, int32_t n_devices, int32_t g, int32_t* col0, int32_t* cols) {
+  if (n <= 0 || n_devices < 1 || n_devices > 8 || g < 0 || g >= n_devices || n % n_devices != 0 || col0 == nullptr ||
+      cols == nullptr)
+    return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  *cols = n / n_devices;
+  *col0 = g * *cols;
+  return CUASR_STATUS_SUCCESS;
+}
+
+int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
+  if (a == nullptr || (a->dtype != CUASR_F32 && a->dtype != CUASR_F64)) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (a->n <= 0 || a->n_devices < 1 || a->n_devices > 8 || a->n % a->n_devices != 0 || a->ldd < a->n)
+    return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (a->devices == nullptr || a->buf0 == nullptr || a->buf1 == nullptr || a->result_buffer == nullptr)
+    return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  const int G = a->n_devices;
+  for (int g = 0; g < G; ++g) {
+    if (a->buf0[g] == nullptr || a->buf1[g] == nullptr) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+    for (int h = 0; h < g; ++h)
+      if (a->devices[g] == a->devices[h]) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  }
+  const int steps = a->iterations > 0 ? a->iterations : std::max(1, ceil_log2(a->n));
+
+  // A reusable barrier of the G host threads that also makes them agree: the thread that completes a round takes
+  // a snapshot of the shared status and every thread of that round gets the same snapshot back, so either all of
+  // them go on or all of them stop (a thread that looked at the status by itself could see a failure of the NEXT
+  // step, leave, and strand the others at the next barrier).
+  std::atomic<int> failed{CUASR_STATUS_SUCCESS};
+  struct Barrier {
+    std::mutex m;
+    std::condition_variable cv;
+    int waiting = 0, generation = 0, count, agreed = CUASR_STATUS_SUCCESS;
+    std::atomic<int>& status;
+    Barrier(int c, std::atomic<int>& st) : count(c), status(st) {}
+    int arrive_and_wait() {
+      std::unique_lock<std::mutex> lock(m);
+      const int gen = generation;
+      if (++waiting == count) {
+        waiting = 0;
+        agreed = status.load();
+        ++generation;
+        cv.notify_all();
+        return agreed;
+      }
+      cv.wait(lock, [&] { return gen != generation; });
+      return agreed;
+    }
+  } barrier(G, failed);
+  auto fail = [&](int status) { int expected = CUASR_STATUS_SUCCESS; failed.compare_exchange_strong(expected, status); };
+
+  auto worker = [&](int g) {
+    bool ok = cudaSetDevice(a->devices[g]) == cudaSuccess;
+    if (!ok) fail(CUASR_STATUS_ERROR_INTERNAL);
+    for (int h = 0; ok && h < G; ++h) {
+      if (h == g) continue;
+      int can = 0;
+      if (cudaDeviceCanAccessPeer(&can, a->devices[g], a->devices[h]) != cudaSuccess || !can) {
+        fail(CUASR_STATUS_ERROR_NOT_SUPPORTED);
+        ok = false;
+        break;
+      }
+      const cudaError_t e = cudaDeviceEnablePeerAccess(a->devices[h], 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+      else if (e != cudaSuccess) { fail(CUASR_STATUS_ERROR_INTERNAL); ok = false; }
+    }
+    cudaStream_t stream = a->streams != nullptr ? static_cast<cudaStream_t>(a->streams[g]) : nullptr;
+    int32_t col0 = 0, cols = 0;
+    cuasr_b200_apsp_multi_partition(a->n, G, g, &col0, &cols);
+    // every GPU has its peers mapped, or somebody failed
+    const bool run = barrier.arrive_and_wait() == CUASR_STATUS_SUCCESS;
+    for (int s = 0; run && s < steps; ++s) {
+      void* const* cur = (s % 2 == 0) ? a->buf0 : a->buf1;
+      void* const* nxt = (s % 2 == 0) ? a->buf1 : a->buf0;
+      void* peers[7];
+      int np = 0;
+      for (int h = 0; h < G; ++h)
+        if (h != g) peers[np++] = nxt[h];
+      cuasr_b200_apsp_shard_args_t sa;
+      std::memset(&sa, 0, sizeof(sa));
+      sa.dtype = a->dtype; sa.n = a->n; sa.col0 = col0; sa.cols = cols;
+      sa.D_cur = cur[g]; sa.ld_cur = a->ldd;
+      sa.D_next = nxt[g]; sa.ld_next = a->ldd;
+      sa.n_peers = np; sa.peer_next = peers;
+      sa.workspace = a->workspace != nullptr ? a->workspace[g] : nullptr;
+      sa.workspace_bytes = sa.workspace != nullptr ? a->workspace_bytes : 0;
+      sa.stream = stream;
+      const int st = cuasr_b200_apsp_shard_squaring(&sa);
+      if (st != CUASR_STATUS_SUCCESS) fail(st);
+      // the step is over when every GPU's kernel, and with it every store into every next iterate, is complete
+      if (cudaStreamSynchronize(stream) != cudaSuccess) fail(CUASR_STATUS_ERROR_INTERNAL);
+      if (barrier.arrive_and_wait() != CUASR_STATUS_SUCCESS) break;   // the same answer on every thread
+    }
+    if (a->device_status != nullptr) a->device_status[g] = cuasr_b200_device_status(stream);
+  };
+
+  std::vector<std::thread> threads;
+  threads.reserve(G);
+  for (int g = 0; g < G; ++g) threads.emplace_back(worker, g);
+  for (auto& t : threads) t.join();
+  *a->result_buffer = steps % 2;
+  return failed.load();
 }
 
 }  // extern "C"

@@ -73,6 +73,45 @@ typedef struct cuasr_b200_apsp_shard_args {
 
 CUASR_B200_API int cuasr_b200_apsp_shard_squaring(const cuasr_b200_apsp_shard_args_t *args);
 
+/* The whole sharded solve by repeated squaring on the GPUs of one machine, from one host process: one host thread
+ * per GPU, plain peer access between the GPUs (no other library), each squaring one
+ * cuasr_b200_apsp_shard_squaring per GPU whose epilogue stores the GPU's block of columns into every GPU's next
+ * iterate, then a barrier of the host threads (each synchronises its own stream first).  Every tensor map a kernel
+ * reads through describes memory of the GPU that runs it; only plain stores cross NVLink.
+ *
+ * The caller owns all memory.  For each of the n_devices (1..8) GPUs, in the order of `devices`:
+ *   buf0[g], buf1[g]   two n x n matrices on device devices[g] (leading dimension ldd, the same everywhere);
+ *                      before the call buf0[g] holds the whole distance matrix on EVERY GPU (the call copies nothing
+ *                      between GPUs but the results of the squarings);
+ *   workspace[g]       optional per-GPU scratch of workspace_bytes (may be NULL; load balance only);
+ *   streams[g]         a stream of device devices[g], or NULL for its default stream.
+ * Columns are dealt out in contiguous blocks of n / n_devices (n must divide).  On return every GPU has finished
+ * and holds the complete closure in buf0[g] or buf1[g]; *result_buffer says which (0 or 1).  The call blocks the
+ * calling host thread until the solve is done.  Status: CUASR_STATUS_ERROR_NOT_SUPPORTED when a GPU cannot reach a
+ * peer's memory, otherwise the first error any GPU met; `device_status` (n_devices entries, may be NULL) receives
+ * each GPU's cuasr_b200_device_status after the solve. */
+typedef struct cuasr_b200_apsp_multi_args {
+  int32_t dtype;            /* CUASR_F32 or CUASR_F64 */
+  int32_t n;
+  int32_t iterations;       /* squarings; 0 = ceil(log2 n) */
+  int32_t n_devices;
+  const int32_t *devices;   /* CUDA device ordinals */
+  void *const *buf0;
+  void *const *buf1;
+  int64_t ldd;
+  void *const *workspace;   /* NULL, or n_devices entries each NULL or a device pointer */
+  size_t workspace_bytes;
+  void *const *streams;     /* NULL, or n_devices entries */
+  int32_t *result_buffer;   /* out */
+  int32_t *device_status;   /* out, may be NULL */
+} cuasr_b200_apsp_multi_args_t;
+
+CUASR_B200_API int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t *args);
+
+/* How the columns are dealt out by cuasr_b200_apsp_multi: first column and number of columns of GPU `g` of
+ * `n_devices`.  Returns 0, or CUASR_STATUS_ERROR_INVALID_PROBLEM when n does not divide or an index is out of range. */
+CUASR_B200_API int cuasr_b200_apsp_multi_partition(int32_t n, int32_t n_devices, int32_t g, int32_t *col0, int32_t *cols);
+
 /* One-sided ordering between GPUs, for solves in which one rank produces what the others consume (the column
  * panels of the sharded Floyd-Warshall solve).  A barrier makes the producer wait for the slowest consumer to
  * arrive; with these two calls the producer only announces, and each consumer waits for the announcement alone.

@@ -39,6 +39,53 @@ def test_argument_checks_need_no_device():
     assert lib.cuasr_b200_apsp_shard_squaring(None) == int(Status.kErrorInvalidProblem)
 
 
+def test_multi_gpu_entry_point_partition_and_argument_checks():
+    """cuasr_b200_apsp_multi: how the columns are dealt out, and what is refused before any GPU is touched."""
+    assert apsp.multi_partition(16384, 8, 0) == (0, 2048)
+    assert apsp.multi_partition(16384, 8, 7) == (14336, 2048)
+    assert apsp.multi_partition(1000, 4, 2) == (500, 250)
+    assert apsp.multi_partition(1000, 3, 0) is None          # n must divide
+    assert apsp.multi_partition(1024, 9, 0) is None          # at most 8 GPUs (one launch has 8 destinations)
+    assert apsp.multi_partition(1024, 2, 2) is None
+    st, _, _ = apsp.multi_device_solve(DType.F32, 1000, [0, 1, 2], [4096] * 3, [8192] * 3)
+    assert st == Status.kErrorInvalidProblem                 # 1000 columns over 3 GPUs
+    st, _, _ = apsp.multi_device_solve(DType.F32, 1024, [0, 0], [4096] * 2, [8192] * 2)
+    assert st == Status.kErrorInvalidProblem                 # the same device twice
+    st, _, _ = apsp.multi_device_solve(DType.F32, 1024, [0, 1], [4096, 0], [8192] * 2)
+    assert st == Status.kErrorInvalidProblem                 # a missing buffer
+    st, _, _ = apsp.multi_device_solve(DType.S32, 1024, [0], [4096], [8192])
+    assert st == Status.kErrorInvalidProblem                 # not a distance type
+    st, _, _ = apsp.multi_device_solve(DType.F32, 1024, [0], [4096], [8192], ldd=1000)
+    assert st == Status.kErrorInvalidProblem
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,ld", [(1024, 1024), (768, 776)])
+def test_multi_gpu_solve_from_one_process(cuda_device, n, ld):
+    """cuasr_b200_apsp_multi on every GPU of the box that divides n (one GPU included: the same code path with no
+    peers): plain cudaMalloc'ed buffers, host threads and peer stores only; the closure must equal the host's."""
+    import torch
+    w = _graph(n, n, np.float32)
+    want = _closure(w)
+    G = torch.cuda.device_count()
+    while n % G:
+        G -= 1
+    G = min(G, 4)
+    buf = np.full((n, ld), 7.0, dtype=np.float32)
+    buf[:, :n] = w.T
+    b0 = [torch.from_numpy(buf).to(f"cuda:{g}") for g in range(G)]
+    b1 = [torch.full((n * ld,), -3.0, dtype=torch.float32, device=f"cuda:{g}") for g in range(G)]
+    for g in range(G):
+        torch.cuda.synchronize(g)
+    st, which, status = apsp.multi_device_solve(DType.F32, n, list(range(G)), [t.data_ptr() for t in b0],
+                                                [t.data_ptr() for t in b1], ldd=ld)
+    assert st == Status.kSuccess and status == [0] * G
+    for g in range(G):
+        got = (b0 if which == 0 else b1)[g].cpu().numpy().reshape(n, ld)
+        assert np.array_equal(got[:, :n].T.astype(np.float64), want), f"GPU {g}"
+    torch.cuda.set_device(0)
+
+
 def _graph(n, seed, dtype):
     rng = np.random.default_rng(seed)
     w = rng.integers(1, 101, size=(n, n)).astype(dtype)
