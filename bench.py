@@ -598,6 +598,96 @@ def apsp_solve_record(wl, rank, world, dev, exchange):
             "parity_spot_check": bool(ok and np.array_equal(host_out.numpy()[: 32 * n], want))}
 
 
+def run_path(args, wl):
+    """Path-tracking product: one step = dist <- min(dist, A (x) B) from dist = +inf with the index of the first best
+    k recorded for every element (cuasr_b200_srgemm_path), single GPU."""
+    import numpy as np
+    import torch
+
+    import oracle
+    from cuasr_b200 import DType, RINGS, Srgemm, Status, device_status, launch_count, srgemm_path
+
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    m, n, k = wl.m, wl.n, wl.k
+    A, B = wl.operand("A", dev), wl.operand("B", dev)
+    D = torch.empty(m * n, dtype=torch.float32, device=dev)
+    P = torch.empty(m * n, dtype=torch.int32, device=dev)
+    op = Srgemm(*RINGS[wl.ring], wl.dtype, *wl.layouts, add_identity=identity_of(wl))
+    stream = torch.cuda.current_stream()
+
+    def step():
+        D.fill_(float("inf")); P.fill_(-1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        st = srgemm_path(op, (m, n, k), (A, m), (B, k), (D, m), (P, m), stream=stream)
+        e1.record(stream)
+        assert st == Status.kSuccess
+        return e0, e1
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    launches0 = launch_count()
+    with ClockSampler(0) as clocks:
+        events = [step() for _ in range(args.steps)]
+        torch.cuda.synchronize()
+    launches = launch_count() - launches0
+    assert device_status() == 0
+    ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    # the same product once more on the finished distances: nothing improves any more (the state of a late
+    # Floyd-Warshall or squaring step), so the index bookkeeping is never entered
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0.record(stream)
+    assert srgemm_path(op, (m, n, k), (A, m), (B, k), (D, m), (P, m), stream=stream) == Status.kSuccess
+    w1.record(stream)
+    torch.cuda.synchronize()
+    settled_ms = w0.elapsed_time(w1)
+    # end to end: operands from pinned host memory, distances and parents back
+    hA = torch.empty(A.numel(), dtype=torch.float32).pin_memory(); hA.copy_(A)
+    hB = torch.empty(B.numel(), dtype=torch.float32).pin_memory(); hB.copy_(B)
+    hD = torch.empty(D.numel(), dtype=torch.float32).pin_memory()
+    hP = torch.empty(P.numel(), dtype=torch.int32).pin_memory()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    A.copy_(hA, non_blocking=True); B.copy_(hB, non_blocking=True)
+    step()
+    hD.copy_(D, non_blocking=True); hP.copy_(P, non_blocking=True)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    # 8 columns against the host routine
+    d0, p0 = np.full(8 * m, np.inf, np.float32), np.full(8 * m, -1, np.int32)
+    t0 = time.perf_counter()
+    want_d, want_p = oracle.srgemm_path(DType.F32, wl.layouts, (m, 8, k), hA.numpy(), m, hB.numpy()[: 8 * k], k, d0, m, p0, m)
+    cpu_sec = time.perf_counter() - t0
+    parity = bool(np.array_equal(hD.numpy()[: 8 * m], want_d) and np.array_equal(hP.numpy()[: 8 * m], want_p))
+    peaks, peak_kind = measured_peaks()
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    peak_tops = sms * 128 * 2 * peaks["sm_max_mhz"] * 1e6 / 1e12
+    achieved = wl.ops / (ms * 1e-3) / 1e12
+    line = {
+        "metric": "minplus_path_f32_srgemm_throughput", "value": round(wl.ops / (ms * 1e-3) / 1e9, 2), "unit": "GOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": dict(workload_config(wl), kernel=op.last_kernel(), l2="operands (128 MiB) exceed the 126 MB L2"),
+        "e2e": {"value": round(wl.ops / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GOP/s", "h2d_bytes_per_step": 4 * (m * k + k * n),
+                "d2h_bytes_per_step": 8 * m * n, "ms_per_step": round(e2e_ms, 3), "steps": 1},
+        "gpu_launches": int(launches), "clocks": clocks.summary(),
+        "roofline": {"bound": "CUDA cores (issue / register-file ports)", "achieved": round(achieved, 3),
+                     "peak": round(peak_tops, 2), "unit": "TOP/s", "frac": round(achieved / peak_tops, 4),
+                     "peak_source": f"{sms} SMs x 128 lanes x 2 x sm_max_mhz ({peak_kind})", "kernel_ms": round(ms, 4),
+                     "kernel_ms_when_nothing_improves": round(settled_ms, 4), "traffic": None},
+        "cpu_baseline": {"value": round(2.0 * m * 8 * k / cpu_sec / 1e9, 3), "unit": "GOP/s", "cores": 1, "kind": "port",
+                         "sample": f"8 columns of D ({2.0 * m * 8 * k / 1e9:.2f} GOP), the scalar path-tracking loop"},
+        "parity_spot_check": parity,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_apsp_fw(args, wl):
     """Blocked Floyd-Warshall workload: one step = one whole APSP solve (2 n^3 semiring operations)."""
     import numpy as np
@@ -854,7 +944,9 @@ def main():
         run_reference(args, wl)
     else:
         args.warmup = max(args.warmup, 3)
-        if wl.name.startswith("apsp_fw"):
+        if wl.path:
+            run_path(args, wl)
+        elif wl.name.startswith("apsp_fw"):
             run_apsp_fw(args, wl)
         elif wl.fill == "apsp":
             run_apsp(args, wl)

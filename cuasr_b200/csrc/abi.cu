@@ -16,6 +16,7 @@
 #include "../../include/cuasr_b200_apsp.h"
 #include "srgemm_launch.h"
 #include "srgemm_path.cuh"
+#include "srgemm_path_tma.cuh"
 
 namespace cuasr_b200 {
 namespace {
@@ -729,6 +730,32 @@ int cuasr_b200_srgemm_path(const cuasr_b200_desc_t* desc, const cuasr_b200_args_
   };
   cudaStream_t stream = static_cast<cudaStream_t>(args->stream);
   cudaError_t err;
+  // fp32 operands TMA can describe take the pipelined kernel; everything else the any-layout one
+  if (desc->dtype == CUASR_F32 && static_cast<long long>(args->m) * args->n >= 64 * 64 && encode_tiled_fn() != nullptr) {
+    const Normalised p = normalise(*desc, *args);
+    const bool dense = p.lda >= (p.a_kcontig ? p.k : p.m) && p.ldb >= (p.b_kcontig ? p.k : p.n);
+    DeviceState* dev = nullptr;
+    CUtensorMap map_a, map_b;
+    if (dense && tma_describable(p.a, p.lda, 4) && tma_describable(p.b, p.ldb, 4) && device_state(&dev) &&
+        make_operand_map<float>(&map_a, static_cast<const float*>(p.a), p.lda, p.m, p.k, p.a_kcontig, true) &&
+        make_operand_map<float>(&map_b, static_cast<const float*>(p.b), p.ldb, p.n, p.k, p.b_kcontig, true)) {
+      PathTmaParams tp;
+      tp.M = p.m; tp.N = p.n; tp.K = p.k;
+      // the normalised problem has a row-major D: element (m, n) at D[m * ldd + n], whatever the caller's layout
+      tp.dist = static_cast<float*>(args->D); tp.d_row = args->ldd; tp.d_col = 1;
+      tp.parent = parent; tp.p_row = ld_parent; tp.p_col = 1;
+      tp.k_offset = k_offset;
+      tp.tiles_m = (p.m + kTileM - 1) / kTileM; tp.tiles_n = (p.n + kTileN - 1) / kTileN;
+      tp.status = dev->status;
+      const long long tiles = static_cast<long long>(tp.tiles_m) * tp.tiles_n;
+      const int grid = static_cast<int>(tiles < dev->sms ? tiles : dev->sms);
+      if (launch_path_tma(maximize, p.a_kcontig, p.b_kcontig, map_a, map_b, tp, grid, stream) != cudaSuccess)
+        return CUASR_STATUS_ERROR_INTERNAL;
+      g_launches.fetch_add(1);
+      t_last_kernel = "path_tma";
+      return CUASR_STATUS_SUCCESS;
+    }
+  }
   if (desc->dtype == CUASR_F32) {
     PathParams<float> pp;
     fill(&pp);

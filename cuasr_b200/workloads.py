@@ -38,6 +38,7 @@ class Workload:
     beta: float = 0.0
     split_k_slices: int = 1
     description: str = ""
+    path: bool = False             # path-tracking product (distances and the index of the best k)
     ld_pad: int = 0                # elements added to the leading dimensions of A and B (an odd value makes them
                                    # operands TMA cannot describe)
 
@@ -86,6 +87,9 @@ WORKLOADS = {w.name: w for w in [
     Workload("minplus_f32_4096_ld4097", "minimum_plus", DType.F32, 4096, 4096, 4096, (COL, COL, COL), "uniform", 0.0, 100.0,
              ld_pad=1, description="min-plus fp32 4096^3 with leading dimension 4097 for A and B: operands TMA cannot "
                                    "describe (the reference accepts any leading dimension)"),
+    Workload("minplus_path_f32_4096", "minimum_plus", DType.F32, 4096, 4096, 4096, (COL, COL, COL), "uniform", 0.0, 100.0,
+             add_identity=math.inf, path=True,
+             description="path-tracking min-plus fp32 4096^3: distances (from +inf) and the first best k of every element"),
     Workload("minplus_f32_512", "minimum_plus", DType.F32, 512, 512, 512, (COL, COL, COL), "uniform", 0.0, 100.0,
              description="config 1: the reference's own CPU-runnable case"),
     Workload("minplus_f64_8192", "minimum_plus", DType.F64, 8192, 8192, 8192, (COL, COL, COL), "graph", 1.0, 1000.0,

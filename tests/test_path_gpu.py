@@ -110,3 +110,69 @@ def test_path_tracking_matches_oracle(cuda_device, dt, maximize):
     x = torch.zeros(16, device="cuda", dtype=torch.float32 if dt == DType.F32 else torch.float64)
     p = torch.zeros(16, device="cuda", dtype=torch.int32)
     assert srgemm_path(bad, (4, 4, 4), (x, 4), (x, 4), (x, 4), (p, 4)) == Status.kErrorNotSupported
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("maximize", [False, True])
+def test_path_tracking_on_the_tma_pipeline(cuda_device, maximize):
+    """fp32 operands TMA can describe (16-byte aligned lines) take the pipelined kernel: all eight layouts, shapes
+    ragged against the 128-wide tiles and the 32-deep K step, integer data (ties everywhere: the first k must win)
+    and real data, existing distances and parents that must survive where nothing improves."""
+    import torch
+    rng = np.random.default_rng(23)
+    dt = DType.F32
+    add_op = Op.MAXIMUM if maximize else Op.MINIMUM
+    for layouts in util.ALL_LAYOUTS:
+        for (m, n, k, integers) in ((128, 128, 64, True), (300, 260, 77, True), (200, 136, 512, False), (64, 64, 33, True)):
+            pad = lambda lay, r, c: (util.extents(lay, r, c)[0] + 3) // 4 * 4      # leading dimensions: multiples of 4
+            A, lda = util.make_matrix(rng, dt, layouts[0], m, k, pad(layouts[0], m, k))
+            B, ldb = util.make_matrix(rng, dt, layouts[1], k, n, pad(layouts[1], k, n))
+            D, ldd = util.make_matrix(rng, dt, layouts[2], m, n, util.extents(layouts[2], m, n)[0] + 1, lo=-4, hi=4)
+            if not integers:
+                A = (A + rng.random(A.size)).astype(np.float32)
+                B = (B + rng.random(B.size)).astype(np.float32)
+            parent = np.full(D.size, -7, np.int32)
+            want_d, want_p = oracle.srgemm_path(dt, layouts, (m, n, k), A, lda, B, ldb, D.copy(), ldd, parent.copy(), ldd,
+                                                k_offset=500, maximize=maximize)
+            dA, dB, dD, dP = (torch.from_numpy(x).cuda() for x in (A, B, D, parent))
+            op = Srgemm(add_op, Op.PLUS, dt, *layouts)
+            assert srgemm_path(op, (m, n, k), (dA, lda), (dB, ldb), (dD, ldd), (dP, ldd), k_offset=500) == Status.kSuccess
+            torch.cuda.synchronize()
+            assert op.last_kernel() == "path_tma", (op.last_kernel(), layouts, m, n, k)
+            assert np.array_equal(dD.cpu().numpy(), want_d), (layouts, m, n, k)
+            assert np.array_equal(dP.cpu().numpy(), want_p), (layouts, m, n, k)
+    assert device_status() == 0
+
+
+@pytest.mark.gpu
+def test_path_tracking_at_4096_sampled(cuda_device):
+    """One 4096^3 path-tracking product on uniform [0, 100) operands (distances start at +inf, parents at -1):
+    distances equal the plain min-plus SRGEMM everywhere; distances and parents of sampled columns equal the host
+    routine."""
+    import torch
+    from cuasr_b200 import Arguments
+    from cuasr_b200.workloads import WORKLOADS
+    wl = WORKLOADS["minplus_f32_4096"]
+    n = wl.n
+    dev = torch.device("cuda", 0)
+    A, B = wl.operand("A", dev), wl.operand("B", dev)
+    D = torch.full((n * n,), float("inf"), dtype=torch.float32, device=dev)
+    P = torch.full((n * n,), -1, dtype=torch.int32, device=dev)
+    op = Srgemm(Op.MINIMUM, Op.PLUS, DType.F32, COL, COL, COL, add_identity=float("inf"))
+    assert srgemm_path(op, (n, n, n), (A, n), (B, n), (D, n), (P, n)) == Status.kSuccess
+    torch.cuda.synchronize()
+    assert op.last_kernel() == "path_tma"
+    plain = torch.empty_like(D)
+    C = torch.full_like(D, float("inf"))
+    assert op(Arguments((n, n, n), (A, n), (B, n), (C, n), (plain, n), (0.0, 0.0))) == Status.kSuccess
+    torch.cuda.synchronize()
+    assert torch.equal(plain, D)
+    hA = A.cpu().numpy()
+    for c0 in (0, 2048, n - 8):
+        hB = wl.operand("B", "cpu", c0 * n, 8 * n).numpy()
+        d0 = np.full(8 * n, np.inf, np.float32)
+        p0 = np.full(8 * n, -1, np.int32)
+        want_d, want_p = oracle.srgemm_path(DType.F32, (COL, COL, COL), (n, 8, n), hA, n, hB, n, d0, n, p0, n)
+        assert np.array_equal(D[c0 * n:(c0 + 8) * n].cpu().numpy(), want_d), c0
+        assert np.array_equal(P[c0 * n:(c0 + 8) * n].cpu().numpy(), want_p), c0
+    assert device_status() == 0
