@@ -5,9 +5,13 @@
 namespace cuasr_b200 {
 template <typename T>
 cudaError_t launch_path(const PathParams<T>& p, bool maximize, cudaStream_t stream) {
-  dim3 grid((p.N + kPathTile - 1) / kPathTile, (p.M + kPathTile - 1) / kPathTile);
-  if (maximize) srgemm_path_kernel<T, true><<<grid, kPathThreads, 0, stream>>>(p);
-  else          srgemm_path_kernel<T, false><<<grid, kPathThreads, 0, stream>>>(p);
+  const long long tiles_m = (p.M + kPathTile - 1) / kPathTile, tiles_n = (p.N + kPathTile - 1) / kPathTile;
+  if (tiles_m * tiles_n > 2147483647LL) return cudaErrorInvalidValue;
+  PathParams<T> q = p;
+  q.tiles_n = static_cast<int>(tiles_n);
+  const unsigned grid = static_cast<unsigned>(tiles_m * tiles_n);
+  if (maximize) srgemm_path_kernel<T, true><<<grid, kPathThreads, 0, stream>>>(q);
+  else          srgemm_path_kernel<T, false><<<grid, kPathThreads, 0, stream>>>(q);
   return cudaGetLastError();
 }
 template <bool kMaximize, bool kAK, bool kBK>

@@ -26,6 +26,7 @@ struct GenericParams {
   // its raw accumulators to partial + z * M * N (row-major, ld N) instead of running the epilogue.
   int k_per_slice;
   T* partial;
+  int tiles_n;               // tiles along N: the tile index runs along grid.x (2^31 - 1 tiles), slices along grid.z
 };
 
 constexpr int kGenTile = 64;     // CTA tile 64 x 64
@@ -41,7 +42,7 @@ srgemm_generic_kernel(GenericParams<typename RingT::Element> p) {
 
   const int tid = threadIdx.x;
   const int tx = tid % 16, ty = tid / 16;
-  const int m0 = blockIdx.y * kGenTile, n0 = blockIdx.x * kGenTile;
+  const int m0 = (blockIdx.x / p.tiles_n) * kGenTile, n0 = (blockIdx.x % p.tiles_n) * kGenTile;
 
   int k_begin = 0, k_end = p.K;
   if (p.partial != nullptr) {

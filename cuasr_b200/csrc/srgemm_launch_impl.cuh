@@ -30,14 +30,19 @@ cudaError_t launch_tma(bool a_kcontig, bool b_kcontig, const CUtensorMap& map_a,
 
 template <int ADD, int MUL, typename T>
 cudaError_t launch_generic(const GenericParams<T>& params, int slices, cudaStream_t stream) {
-  dim3 grid((params.N + kGenTile - 1) / kGenTile, (params.M + kGenTile - 1) / kGenTile, slices);
-  srgemm_generic_kernel<Ring<ADD, MUL, T>><<<grid, kGenThreads, 0, stream>>>(params);
+  const long long tiles_m = (params.M + kGenTile - 1) / kGenTile, tiles_n = (params.N + kGenTile - 1) / kGenTile;
+  if (tiles_m * tiles_n > 2147483647LL || slices > 65535) return cudaErrorInvalidValue;
+  GenericParams<T> p = params;
+  p.tiles_n = static_cast<int>(tiles_n);
+  dim3 grid(static_cast<unsigned>(tiles_m * tiles_n), 1, slices);
+  srgemm_generic_kernel<Ring<ADD, MUL, T>><<<grid, kGenThreads, 0, stream>>>(p);
   return cudaGetLastError();
 }
 
 template <int ADD, int MUL, typename T>
 cudaError_t launch_generic_reduce(const GenericParams<T>& params, int slices, cudaStream_t stream) {
   const long long total = static_cast<long long>(params.M) * params.N;
+  if ((total + 255) / 256 > 2147483647LL) return cudaErrorInvalidValue;
   const int blocks = static_cast<int>((total + 255) / 256);
   splitk_reduce_kernel<Ring<ADD, MUL, T>><<<blocks, 256, 0, stream>>>(params, slices);
   return cudaGetLastError();

@@ -19,6 +19,7 @@ struct PathParams {
   T* dist;     long long d_row, d_col;     // in/out
   int32_t* parent; long long p_row, p_col; // in/out
   int k_offset;                            // added to the recorded k
+  int tiles_n;                             // tiles along N; the tile index runs along grid.x
 };
 
 constexpr int kPathTile = 64;
@@ -31,7 +32,7 @@ srgemm_path_kernel(PathParams<T> p) {
   __shared__ T As[kPathK][kPathTile + 1];
   __shared__ T Bs[kPathK][kPathTile + 1];
   const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
-  const int m0 = blockIdx.y * kPathTile, n0 = blockIdx.x * kPathTile;
+  const int m0 = (blockIdx.x / p.tiles_n) * kPathTile, n0 = (blockIdx.x % p.tiles_n) * kPathTile;
 
   T acc[4][4];
   int32_t idx[4][4];

@@ -90,8 +90,13 @@ CUASR_B200_API int cuasr_b200_srgemm(const cuasr_b200_desc_t *desc, const cuasr_
  *    K, their pieces fill the SMs, and the CTA that finishes a tile last folds the pieces in a fixed order;
  *  - fp32 min/max-plus and min/max-times rings: operands whose contiguous dimension is not K are first copied into
  *    K-contiguous scratch (a bandwidth-bound pre-pass of well under 1 % of the run time), which lets the kernel use
- *    packed fp32x2 adds for both products of a three-input min/max.
- * Needs a current device. */
+ *    packed fp32x2 adds for both products of a three-input min/max;
+ *  - operands the fast kernel cannot read in place are copied into scratch it can read: an operand whose address
+ *    or leading dimension is not a multiple of 16 bytes (the reference accepts alignment 1,
+ *    device/default_srgemm_configuration.h:88-89; without the workspace such a product runs on the slower generic
+ *    kernel), and both operands of an integer min/max ring whose K is not a multiple of the kernel's K step (the
+ *    copies are extended along K: A by the additive identity, B by the multiplicative one).
+ * The size depends on the operand addresses in `args`.  Needs a current device. */
 CUASR_B200_API size_t cuasr_b200_srgemm_optional_workspace_size(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 
 /* cuasr_b200_srgemm whose epilogue also stores every element of D to `n_extra` (at most 7) further
@@ -109,7 +114,9 @@ CUASR_B200_API int cuasr_b200_srgemm_push(const cuasr_b200_desc_t *desc, const c
  * (test/regress/include/fwgpu/cpu_srgemm.hpp:20-48), generalised to both layouts, M x N x K and max-plus.
  * desc: add_op MINIMUM or MAXIMUM, mul_op PLUS, dtype F32 or F64.  args: A, B, D (= the distances, read and
  * written; C, alpha, beta, workspace are ignored), split_k_slices = 1.  parent has D's layout, leading dimension
- * ld_parent, 32-bit signed entries. */
+ * ld_parent, 32-bit signed entries.  fp32 operands with 16-byte aligned storage lines run on the TMA pipeline (the
+ * index update is entered only for rows of the register tile in which some element improved), everything else on
+ * an any-layout kernel. */
 CUASR_B200_API int cuasr_b200_srgemm_path(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args, int32_t *parent,
                                           int64_t ld_parent, int32_t k_offset);
 
@@ -117,7 +124,10 @@ CUASR_B200_API int cuasr_b200_srgemm_path(const cuasr_b200_desc_t *desc, const c
  * (device/srgemm_splitk_parallel.h:220-235, :238-279, :333-348).  The reference needs
  * sizeof(element) * M * N * slices bytes of workspace and two launches; this library needs a little more
  * (per-tile arrival counters) and one launch: the CTA that completes a tile last combines the slices
- * in slice order and applies the epilogue. */
+ * in slice order and applies the epilogue.  Where the slice count leaves SMs idle (tiles x slices below or badly
+ * off a multiple of the SM count) and (+) is exact and order-independent (everything but floating-point plus), every
+ * slice is cut into up to 8 pieces of consecutive K; the workspace size reported with a current device has room
+ * for that, a workspace of only the reference's size is accepted and limits the cutting. */
 CUASR_B200_API int cuasr_b200_srgemm_splitk_can_implement(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 CUASR_B200_API size_t cuasr_b200_srgemm_splitk_workspace_size(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 CUASR_B200_API int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
@@ -141,7 +151,12 @@ CUASR_B200_API int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t *desc, const
  *    with that device current); make that first call before starting any stream capture;
  *  - every call on a device shares the one array, which keeps whatever the previous call left in it: the
  *    counters are cleared on the stream at the start of each call, the partials are fully overwritten
- *    before they are read; two calls that overlap on the GPU (different streams) race on it -- serialise them. */
+ *    before they are read; two calls that overlap on the GPU (different streams) race on it -- serialise them.
+ *    That holds for a call with split_k_slices == 1 too: it hands the array to the ordinary path as its optional
+ *    workspace (balanced last wave, re-packed operands), so it also writes the array;
+ *  - the address found by the first call is kept for the life of the process.  Do not destroy the device's
+ *    context in between (cudaDeviceReset): the array would be loaded anew at another address and later calls
+ *    would write through the old one. */
 #define CUASR_B200_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u + 4096u)
 CUASR_B200_API int cuasr_b200_srgemm_splitk_static(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 

@@ -84,7 +84,8 @@ def fwgemm_outputs():
 
 
 def main():
-    reference = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CUASR_REFERENCE", "/root/reference")
+    reference = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CUASR_REFERENCE")
+    assert reference, "usage: make_golden.py <reference checkout>   (or set CUASR_REFERENCE)"
     assert oracle.have_ref(), "build oracle/_ref first: make -C oracle ref"
     with open(os.path.join(HERE, "regress_known_answer.json"), "w") as f:
         json.dump(known_answer(reference), f, indent=1)

@@ -443,3 +443,22 @@ def test_status_codes(cuda_device):
     needs = Arguments((64, 64, 64), (x, 64), (x, 64), (None, 64), (x, 64), (0.0, 0.0))
     assert op(needs) == Status.kErrorInvalidProblem
     assert device_status() == 0
+
+
+def test_extents_beyond_the_grid_y_limit(cuda_device):
+    """The reference accepts any extent.  A 4.3-million-row product with N = K = 1 has more 64-row tiles than the
+    65535 a CUDA grid allows along y or z; tiles are numbered along x here, so it runs (on the generic kernel: a
+    leading dimension of 1 is nothing TMA can describe)."""
+    import torch
+    m, n, k = 4_300_000, 1, 1
+    g = torch.Generator(device="cuda").manual_seed(3)
+    A = torch.randint(-8, 9, (m,), generator=g, device="cuda").float()
+    B = torch.tensor([2.0], device="cuda")
+    C = torch.randint(-8, 9, (m,), generator=g, device="cuda").float()
+    D = torch.zeros(m, device="cuda")
+    op = Srgemm(*RINGS["minimum_plus"], DType.F32, ROW, ROW, ROW)
+    assert op(Arguments((m, n, k), (A, 1), (B, 1), (C, 1), (D, 1), (0.0, 0.0))) == Status.kSuccess
+    torch.cuda.synchronize()
+    assert op.last_kernel() == "generic"
+    assert torch.equal(D, torch.minimum(A + 2.0, C))
+    assert device_status() == 0
