@@ -168,7 +168,6 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           float lo[8], hi[8], next[8];
-          bool changed = false;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             if constexpr (kAK && kBK) {
@@ -178,9 +177,15 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
               hi[j] = a[i][1] + b[j][1];
             }
             next[j] = best3(acc[i][j], lo[j], hi[j]);
-            changed = changed || better(next[j], acc[i][j]);
           }
-          if (changed) {
+          // "did any of the eight change": the folds only ever move a value in one direction, so the bit patterns
+          // differ exactly where a value improved; eight independent XORs and an OR tree instead of a chain of
+          // dependent compares
+          uint32_t diff[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) diff[j] = __float_as_uint(next[j]) ^ __float_as_uint(acc[i][j]);
+          const uint32_t any = ((diff[0] | diff[1]) | (diff[2] | diff[3])) | ((diff[4] | diff[5]) | (diff[6] | diff[7]));
+          if (any != 0) {
             // something in this row improved: replay its two k steps in order to see which one it was
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
