@@ -409,7 +409,7 @@ def run_ours(args, wl):
     if wl.split_k_slices == 1 and not wl.ld_pad:
         extra_fn = (lambda j, byte_off: [p + off + byte_off for r, p in enumerate(peer_d) if r != rank]) if push else None
         pipe = HostSrgemm(op, m, cols if world > 1 else n, k, wl.alpha, wl.beta, dev,
-                          chunks=8 if world == 1 else max(1, min(8, cols // 512)),
+                          chunks=args.e2e_chunks or (8 if world == 1 else max(1, min(8, cols // 512))),
                           extra_outputs_per_chunk=extra_fn, buffers=(A, B, Cs, Ds),
                           group=dist.group.WORLD if world > 1 else None, rank=rank, world=world)
     if pipe is not None and world > 1:
@@ -930,6 +930,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="minplus_f32_8192")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--e2e-chunks", type=int, default=0,
+                    help="column chunks of the end-to-end (host buffer) step; 0 = 8 on one GPU, 512-column chunks beyond")
     ap.add_argument("--no-workspace", action="store_true",
                     help="do not hand the library the optional workspace (no balanced last wave, no re-packed operands)")
     ap.add_argument("--no-apsp", action="store_true",

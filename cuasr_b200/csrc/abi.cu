@@ -304,10 +304,10 @@ struct ExtraOutputs {
 // Re-packing of MN-contiguous fp32 operands into K-contiguous scratch, so that the kernel variant with packed
 // fp32x2 adds (both operands deliver (k, k+1) register pairs) can run.  Worth it only for the rings that variant
 // speeds up, for problems large enough for the TMA kernel, and when the copy is cheap against what it buys: the
-// variant saves about 2 % of the 2 m n k operations, the copy moves 8 bytes per re-packed element, which breaks even
-// near m n = 1000 x (re-packed rows).  A thin slice of a large product (one rank's share of a sharded SRGEMM, one
-// chunk of the host pipeline: 8192 x 1024 x 8192 measured 4.38 ms without and 4.50 ms with the copy) fails that test;
-// copies of less than 16 MB are always taken (512^3: 0.076 -> 0.050 ms).
+// variant is about 7 % faster (8192^3: 31.0 ms against 33.4), the copy moves 8 bytes per re-packed element, which
+// breaks even near m n = 700 x (re-packed rows).  One rank's share of a sharded SRGEMM or one chunk of the host
+// pipeline (8192 x 1024 x 8192) passes that test, thinner slices do not; copies of less than 16 MB are always taken
+// (512^3: 0.076 -> 0.050 ms).
 bool repack_pays(const cuasr_b200_desc_t& desc, const Normalised& p) {
   const bool ring = (desc.add_op == CUASR_OP_MINIMUM || desc.add_op == CUASR_OP_MAXIMUM) &&
                     (desc.mul_op == CUASR_OP_PLUS || desc.mul_op == CUASR_OP_MULTIPLIES);
@@ -316,7 +316,7 @@ bool repack_pays(const cuasr_b200_desc_t& desc, const Normalised& p) {
     return false;
   const long long rows = (p.a_kcontig ? 0LL : p.m) + (p.b_kcontig ? 0LL : p.n);
   const bool small_copy = rows * p.k < 4LL * 1024 * 1024;
-  return small_copy || static_cast<long long>(p.m) * p.n >= 2048LL * rows;
+  return small_copy || static_cast<long long>(p.m) * p.n >= 700LL * rows;
 }
 // Which operands a launch copies into K-contiguous, 16-byte aligned scratch before the TMA kernel runs:
 //   * an operand TMA cannot describe (its address or its leading dimension is not a multiple of 16 bytes; the

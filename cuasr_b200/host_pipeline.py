@@ -16,9 +16,15 @@ chunk is computed piece by piece, `D <- (alpha (x) A_p (x)(+) B_p) (+) D`, each 
 (plus-times on floats keeps the one-piece schedule).
 
 Several ranks that shard the output (each computes its own lines of D) all need the shared operand.  With `group`
-set, every rank brings only its 1/world share of each K piece over its own host link and an all-gather over NVLink
-completes the piece on every GPU, so each byte of the shared operand crosses a host link once per node and the
-first chunk still starts after the first piece.
+set, every rank brings only its 1/world share of each K piece over its own host link and the ranks complete the
+piece on every GPU over NVLink, so each byte of the shared operand crosses a host link once per node and the
+first chunk still starts after the first piece.  Two ways to complete a piece (`exchange`):
+  "p2p"   the shared operand lives in symmetric memory; a rank copies its share into every peer's buffer with plain
+          device-to-device copies (copy engines) and raises a word on each peer (cuasr_b200_flag_raise); a rank's
+          compute stream waits until the words of all ranks have arrived (cuasr_b200_flag_wait, bounded).  No SM is
+          needed, which matters because the SRGEMM kernel is persistent and fills every SM: a collective kernel
+          would have to wait for it, and piece p + 1 could not arrive while piece p computes.
+  "nccl"  an NCCL all-gather per piece on a communication stream.
 """
 from __future__ import annotations
 
@@ -35,13 +41,15 @@ def _address(ref) -> int:
 class HostSrgemm:
     def __init__(self, operator: Srgemm, m: int, n: int, k: int, alpha, beta, device, chunks: int = 8,
                  extra_outputs_per_chunk=None, buffers=None, shared_on_device: bool = False, group=None,
-                 rank: int = 0, world: int = 1):
+                 rank: int = 0, world: int = 1, exchange: str = "p2p"):
         """shared_on_device: the operand every chunk needs (A for a column-major D) is already in its device buffer
         when the call starts; it is not copied here.
         group, rank, world: torch.distributed group whose ranks all need the same shared operand (m, n, k describe
         THIS rank's product).  The host tensor passed for the shared operand then holds this rank's share only:
         for each of the `k_pieces` K pieces in turn, the rank-th of `world` equal parts of that piece's storage
-        (`shared_share_layout` gives the element ranges)."""
+        (`shared_share_layout` gives the element ranges).  exchange: "p2p" or "nccl", see the module docstring;
+        with "p2p" the shared operand is kept in symmetric memory allocated here (the matching entry of `buffers`
+        is not used)."""
         import torch
 
         self.torch = torch
@@ -51,11 +59,14 @@ class HostSrgemm:
         # the chunked dimension must be the line dimension of C and of the operand that shares it
         self.chunkable = (col_c and lb == Layout.COLUMN_MAJOR) or (not col_c and la == Layout.ROW_MAJOR)
         lines = n if col_c else m
-        self.chunks = max(1, min(chunks, lines // 128)) if self.chunkable else 1
-        while lines % self.chunks:
-            self.chunks -= 1
         self.col_c = col_c
         self.es = 8 if operator.dtype == DType.F64 else 4
+        count = max(1, min(int(chunks), lines // 128)) if self.chunkable else 1
+        while lines % count:
+            count -= 1
+        self.chunk_lines = [lines // count] * count
+        self.chunks = len(self.chunk_lines)
+        self.chunk_start = [sum(self.chunk_lines[:j]) for j in range(self.chunks)]
         tdt = {DType.F32: torch.float32, DType.F64: torch.float64, DType.S32: torch.int32, DType.U32: torch.int32}[operator.dtype]
         if buffers is not None:      # device storage supplied by the caller: flat A (m*k), B (k*n), C and D (m*n)
             self.dA, self.dB, self.dC, self.dD = buffers
@@ -89,7 +100,33 @@ class HostSrgemm:
                 self.k_pieces = 1
             if shared_elems % (self.k_pieces * self.world):
                 raise ValueError("the shared operand does not divide into equal shares for the ranks")
+            if exchange not in ("p2p", "nccl"):
+                raise ValueError(exchange)
             self.s_comm = torch.cuda.Stream(device=device)
+            self.exchange = exchange
+            self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+            if exchange == "p2p":
+                import torch.distributed as dist
+                import torch.distributed._symmetric_memory as symm_mem
+                grp = dist.group.WORLD if group is None else group
+                shared = symm_mem.empty(shared_elems, dtype=tdt, device=device)
+                handle = symm_mem.rendezvous(shared, grp)
+                # views of every rank's copy of the shared operand (element r is this rank's own buffer for r == rank)
+                self._peer_shared = [handle.get_buffer(r, (shared_elems,), tdt) for r in range(self.world)]
+                if col_c:
+                    self.dA = shared
+                else:
+                    self.dB = shared
+                # arrival words: word p * world + r = "rank r's share of piece p has been delivered", per call epoch
+                self._sig = symm_mem.empty(64, dtype=torch.int32, device=device)
+                self._sig_handle = symm_mem.rendezvous(self._sig, grp)
+                self._peer_sig = [int(ptr) for ptr in self._sig_handle.buffer_ptrs]
+                self._handles = (handle, self._sig_handle)
+                self._sig.zero_()
+                torch.cuda.synchronize(device)
+                dist.barrier(group=group)
+                self._epoch = 0
+                self.wait_ms = 5000
 
     def shared_share_layout(self):
         """Element ranges [(start, stop), ...] of the shared operand's flat storage that make up this rank's share,
@@ -98,6 +135,17 @@ class HostSrgemm:
         piece = shared_elems // self.k_pieces
         sub = piece // self.world
         return [(p * piece + self.rank * sub, p * piece + (self.rank + 1) * sub) for p in range(self.k_pieces)]
+
+    def _open_exchange(self, start) -> None:
+        """Start of a call with several ranks.  With the p2p exchange the peers are about to write into this rank's
+        copy of the shared operand: nobody may send before everybody has finished computing on the previous
+        contents, i.e. has reached this point on its device (a one-word collective on the communication stream)."""
+        self.s_comm.wait_event(start)
+        if self.exchange == "p2p":
+            import torch.distributed as dist
+            self._epoch += 1
+            with self.torch.cuda.stream(self.s_comm):
+                dist.all_reduce(self._flag, group=self.group)
 
     def _bring_shared_piece(self, shared_dev, shared_host, p: int):
         """Starts the transfer of K piece p of the shared operand and returns the event that marks its arrival on
@@ -121,24 +169,40 @@ class HostSrgemm:
             copied.record(self.s_in)
         with torch.cuda.stream(self.s_comm):
             self.s_comm.wait_event(copied)
-            dist.all_gather_into_tensor(shared_dev[p * piece:(p + 1) * piece], shared_dev[mine], group=self.group)
+            if self.exchange == "nccl":
+                dist.all_gather_into_tensor(shared_dev[p * piece:(p + 1) * piece], shared_dev[mine], group=self.group)
+            else:
+                import ctypes
+
+                from . import _lib
+                lib = _lib.load()
+                for r in range(self.world):
+                    if r != self.rank:
+                        self._peer_shared[r][mine].copy_(shared_dev[mine], non_blocking=True)
+                word = 4 * (p * self.world + self.rank)
+                ptrs = (ctypes.c_void_p * self.world)(*[ptr + word for ptr in self._peer_sig])
+                st = lib.cuasr_b200_flag_raise(ptrs, self.world, self._epoch, self.s_comm.cuda_stream)
+                if st == 0:
+                    st = lib.cuasr_b200_flag_wait(self._sig.data_ptr() + 4 * p * self.world, self.world, self._epoch,
+                                                  self.wait_ms, self.s_comm.cuda_stream)
+                if st != 0:
+                    raise RuntimeError(f"exchange of the shared operand failed: {Status(st)!r}")
             arrived.record(self.s_comm)
         return arrived
 
     def _chunk_args(self, j: int):
         """Arguments of chunk j and the element ranges of B (or A), C and D it touches."""
         m, n, k = self.m, self.n, self.k
+        w, l0 = self.chunk_lines[j], self.chunk_start[j]
         if self.col_c:
-            w = n // self.chunks
-            moving, fixed = slice(j * w * k, (j + 1) * w * k), None       # columns of B
-            out = slice(j * w * m, (j + 1) * w * m)
+            moving, fixed = slice(l0 * k, (l0 + w) * k), None             # columns of B
+            out = slice(l0 * m, (l0 + w) * m)
             args = Arguments((m, w, k), (self.dA, self.lda), (self.dB.data_ptr() + moving.start * self.es, self.ldb),
                              (self.dC.data_ptr() + out.start * self.es, self.ldc),
                              (self.dD.data_ptr() + out.start * self.es, self.ldc), (self.alpha, self.beta))
         else:
-            w = m // self.chunks
-            moving = slice(j * w * k, (j + 1) * w * k)                     # rows of A
-            out = slice(j * w * n, (j + 1) * w * n)
+            moving = slice(l0 * k, (l0 + w) * k)                           # rows of A
+            out = slice(l0 * n, (l0 + w) * n)
             args = Arguments((w, n, k), (self.dA.data_ptr() + moving.start * self.es, self.lda), (self.dB, self.ldb),
                              (self.dC.data_ptr() + out.start * self.es, self.ldc),
                              (self.dD.data_ptr() + out.start * self.es, self.ldc), (self.alpha, self.beta))
@@ -198,10 +262,10 @@ class HostSrgemm:
                 with torch.cuda.stream(self.s_in):
                     shared_dev.copy_(shared_host, non_blocking=True)
             else:
-                self.s_comm.wait_event(start)
+                self._open_exchange(start)
                 whole_shared = self._bring_shared_piece(shared_dev, shared_host, 0)
         elif self.world > 1:
-            self.s_comm.wait_event(start)
+            self._open_exchange(start)
         for j in range(self.chunks):
             args, moving, out = self._chunk_args(j)
             with torch.cuda.stream(self.s_in):

@@ -162,7 +162,7 @@ def test_multi_gpu_apsp(mode):
         assert np.array_equal(out[(mode, rank)], want), f"{mode}: rank {rank} differs from the CPU solve"
 
 
-def _host_pipeline_rank(rank, world, port, m, n, k, out):
+def _host_pipeline_rank(rank, world, port, m, n, k, exchange, out):
     """One rank of a sharded host-buffer SRGEMM: its columns of D, its columns of B, its share of every K piece of A."""
     import torch
     import torch.distributed as dist
@@ -178,7 +178,8 @@ def _host_pipeline_rank(rank, world, port, m, n, k, out):
     cols = n // world
     col = Layout.COLUMN_MAJOR
     op = Srgemm(*RINGS["minimum_plus"], DType.F32, col, col, col)
-    pipe = HostSrgemm(op, m, cols, k, 0.0, 0.0, dev, chunks=2, group=dist.group.WORLD, rank=rank, world=world)
+    pipe = HostSrgemm(op, m, cols, k, 0.0, 0.0, dev, chunks=2, group=dist.group.WORLD, rank=rank, world=world,
+                      exchange=exchange)
     share = torch.cat([A[a:b] for a, b in pipe.shared_share_layout()]).pin_memory()
     hB = B[rank * cols * k:(rank + 1) * cols * k].clone().pin_memory()
     hC = C[rank * cols * m:(rank + 1) * cols * m].clone().pin_memory()
@@ -194,9 +195,11 @@ def _host_pipeline_rank(rank, world, port, m, n, k, out):
     dist.destroy_process_group()
 
 
-def test_multi_gpu_host_buffer_pipeline():
-    """Ranks that shard the columns of D bring 1/world of every K piece of A each and complete the pieces with
-    all-gathers; the result is the one-shot host SRGEMM's, bit for bit."""
+@pytest.mark.parametrize("exchange", ["p2p", "nccl"])
+def test_multi_gpu_host_buffer_pipeline(exchange):
+    """Ranks that shard the columns of D bring 1/world of every K piece of A each and complete the pieces over
+    NVLink (peer copies + arrival words, or NCCL all-gathers); the result is the one-shot host SRGEMM's, bit for
+    bit."""
     import torch
     import torch.multiprocessing as mp
     import oracle
@@ -209,7 +212,7 @@ def test_multi_gpu_host_buffer_pipeline():
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     out = mp.Manager().dict()
-    mp.spawn(_host_pipeline_rank, args=(world, port, m, n, k, out), nprocs=world, join=True)
+    mp.spawn(_host_pipeline_rank, args=(world, port, m, n, k, exchange, out), nprocs=world, join=True)
     g = torch.Generator().manual_seed(1234)
     A = torch.randint(-8, 9, (m * k,), generator=g).float().numpy()
     B = torch.randint(-8, 9, (k * n,), generator=g).float().numpy()
