@@ -165,37 +165,43 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
         }
         const int32_t k0 = kt * TK + step * 2 + p.k_offset;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float lo[8], hi[8], next[8];
+        // The rows are software-pipelined by one: the folds of row i + 1 are issued before the test on row i, so
+        // that the chain add -> fold -> "anything changed?" -> branch of one row runs under the arithmetic of the next.
+        float lo[2][8], hi[2][8], next[2][8];
+        uint32_t any[2];
+        auto fold_row = [&](int i, int buf) {
+          uint32_t diff[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             if constexpr (kAK && kBK) {
-              unpack2(add2(pack2(a[i][0], a[i][1]), pack2(b[j][0], b[j][1])), lo[j], hi[j]);
+              unpack2(add2(pack2(a[i][0], a[i][1]), pack2(b[j][0], b[j][1])), lo[buf][j], hi[buf][j]);
             } else {
-              lo[j] = a[i][0] + b[j][0];
-              hi[j] = a[i][1] + b[j][1];
+              lo[buf][j] = a[i][0] + b[j][0];
+              hi[buf][j] = a[i][1] + b[j][1];
             }
-            next[j] = best3(acc[i][j], lo[j], hi[j]);
+            next[buf][j] = best3(acc[i][j], lo[buf][j], hi[buf][j]);
+            // the folds only ever move a value in one direction, so the bit patterns differ exactly where a
+            // value improved
+            diff[j] = __float_as_uint(next[buf][j]) ^ __float_as_uint(acc[i][j]);
           }
-          // "did any of the eight change": the folds only ever move a value in one direction, so the bit patterns
-          // differ exactly where a value improved; eight independent XORs and an OR tree instead of a chain of
-          // dependent compares
-          uint32_t diff[8];
+          any[buf] = ((diff[0] | diff[1]) | (diff[2] | diff[3])) | ((diff[4] | diff[5]) | (diff[6] | diff[7]));
+        };
+        fold_row(0, 0);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) diff[j] = __float_as_uint(next[j]) ^ __float_as_uint(acc[i][j]);
-          const uint32_t any = ((diff[0] | diff[1]) | (diff[2] | diff[3])) | ((diff[4] | diff[5]) | (diff[6] | diff[7]));
-          if (any != 0) {
+        for (int i = 0; i < 8; ++i) {
+          const int buf = i & 1;
+          if (i + 1 < 8) fold_row(i + 1, buf ^ 1);
+          if (any[buf] != 0) {
             // something in this row improved: replay its two k steps in order to see which one it was
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float cur = acc[i][j];
-              if (better(lo[j], cur)) { cur = lo[j]; idx[i][j] = k0; }
-              if (better(hi[j], cur)) { idx[i][j] = k0 + 1; }
+              if (better(lo[buf][j], cur)) { cur = lo[buf][j]; idx[i][j] = k0; }
+              if (better(hi[buf][j], cur)) { idx[i][j] = k0 + 1; }
             }
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[i][j] = next[j];
+          for (int j = 0; j < 8; ++j) acc[i][j] = next[buf][j];
         }
       }
       __syncwarp();
