@@ -2,7 +2,8 @@
 // loads only), packed fp32x2 arithmetic and three-input min/max.
 //
 // Every wait is bounded: a wait that runs out of attempts records a code in a device-side status word
-// and returns false, and callers unwind instead of spinning forever.
+// and the waiter stops waiting (the producer returns; consumer warps go through mbar_wait_or_abandon, which lets
+// all of them finish their loops so that no warp is left alone at a barrier) instead of spinning forever.
 #pragma once
 
 #include <cstdint>
@@ -74,6 +75,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
   }
   report_device_error(status, code_on_timeout);
   return false;
+}
+
+// The consumers' form of the wait.  Consumer warps of a CTA meet at named barriers (split tiles), so one of them
+// must not leave while the others go on.  When a wait runs out here, the code is recorded and a flag in shared
+// memory is raised; from then on every wait of the CTA that does not succeed at once returns after a few attempts,
+// and all warps finish their loops on whatever the stages hold.  The result of such a launch is void and the status
+// word says so; what matters is that the kernel ends.
+__device__ __forceinline__ void mbar_wait_or_abandon(uint64_t* bar, uint32_t parity, unsigned int* status,
+                                                     unsigned int code_on_timeout, volatile unsigned int* abandoned) {
+  if (mbar_try_wait(bar, parity)) return;
+  for (uint32_t i = 0; i < kMaxWaitAttempts; ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 63) == 63 && *abandoned != 0) return;
+  }
+  report_device_error(status, code_on_timeout);
+  *abandoned = 1;
 }
 
 // 2-D tiled TMA load into this CTA's shared memory, completion signalled on `bar`.

@@ -47,6 +47,7 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
   uint64_t* empty_bar = full_bar + kStages;
+  volatile unsigned int* abandoned = reinterpret_cast<unsigned int*>(empty_bar + kStages);   // see ptx.cuh
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   if (threadIdx.x == 0) {
@@ -54,6 +55,7 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], kConsumerWarps);
     }
+    *abandoned = 0;
     fence_barrier_init();
   }
   __syncthreads();
@@ -122,7 +124,7 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
     for (int kt = 0; kt < k_tiles; ++kt, ++it) {
       const int s = it % kStages;
-      if (!mbar_wait(&full_bar[s], (it / kStages) & 1, p.status, kDeviceTimeoutFull)) return;
+      mbar_wait_or_abandon(&full_bar[s], (it / kStages) & 1, p.status, kDeviceTimeoutFull, abandoned);
       const uint32_t sa = smem_base + s * kStageBytes;
       const uint32_t sb = sa + kOperandStageBytes;
 #pragma unroll 1

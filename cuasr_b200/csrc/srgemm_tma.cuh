@@ -130,6 +130,7 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_smem + kEpilogueBytes);
   uint64_t* empty_bar = full_bar + kStages;
   unsigned int* ticket_smem = reinterpret_cast<unsigned int*>(empty_bar + kStages);
+  volatile unsigned int* abandoned = ticket_smem + 1;     // raised when a consumer's wait ran out (see ptx.cuh)
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
@@ -138,6 +139,7 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], kConsumerWarps);
     }
+    *abandoned = 0;
     fence_barrier_init();
   }
   __syncthreads();
@@ -242,7 +244,7 @@ srgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 
     for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
       const int s = it % kStages;
-      if (!mbar_wait(&full_bar[s], (it / kStages) & 1, p.status, kDeviceTimeoutFull)) return;
+      mbar_wait_or_abandon(&full_bar[s], (it / kStages) & 1, p.status, kDeviceTimeoutFull, abandoned);
       const uint32_t sa = smem_base + s * kStageBytes;
       const uint32_t sb = sa + kOperandStageBytes;
 
