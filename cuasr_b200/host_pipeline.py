@@ -34,6 +34,17 @@ from .semiring import DType, Layout, Op, Status
 from .srgemm import Arguments, Srgemm
 
 
+def share_ranges(shared_elems: int, k_pieces: int, rank: int, world: int):
+    """Element ranges [(start, stop), ...] of the shared operand's flat storage that rank `rank` of `world` brings
+    over its own host link: the rank-th of `world` equal parts of each of the `k_pieces` K pieces, in piece order.
+    The ranges of all ranks tile the operand exactly once."""
+    if shared_elems % (k_pieces * world):
+        raise ValueError("the shared operand does not divide into equal shares for the ranks")
+    piece = shared_elems // k_pieces
+    sub = piece // world
+    return [(p * piece + rank * sub, p * piece + (rank + 1) * sub) for p in range(k_pieces)]
+
+
 def _address(ref) -> int:
     return ref.data_ptr() if hasattr(ref, "data_ptr") else int(ref)
 
@@ -132,9 +143,7 @@ class HostSrgemm:
         """Element ranges [(start, stop), ...] of the shared operand's flat storage that make up this rank's share,
         in the order the share's host tensor holds them (one range per K piece)."""
         shared_elems = (self.m * self.k) if self.col_c else (self.k * self.n)
-        piece = shared_elems // self.k_pieces
-        sub = piece // self.world
-        return [(p * piece + self.rank * sub, p * piece + (self.rank + 1) * sub) for p in range(self.k_pieces)]
+        return share_ranges(shared_elems, self.k_pieces, self.rank, self.world)
 
     def _open_exchange(self, start) -> None:
         """Start of a call with several ranks.  With the p2p exchange the peers are about to write into this rank's

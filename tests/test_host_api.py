@@ -1,6 +1,7 @@
 """Host-side logic of the C ABI that needs no GPU: argument validation, status codes and workspace sizes, called
 through the library with made-up (never dereferenced) pointers."""
 import numpy as np
+import pytest
 
 from cuasr_b200 import Arguments, DType, Layout, Op, Srgemm, SrgemmSplitKParallel, Status, annihilator, identity
 
@@ -85,3 +86,22 @@ def test_run_before_initialize_and_update():
     assert op.initialize(args(slices=2)) == Status.kErrorInvalidProblem
     assert op.initialize(args()) == Status.kSuccess
     assert op.update(args(a=P + 4096)) == Status.kSuccess
+
+
+def test_shares_of_the_shared_operand_tile_it_exactly_once():
+    """Sharded host-buffer SRGEMM: every rank brings 1/world of every K piece of the operand all ranks need; together
+    the shares must cover the operand once, piece by piece, and a rank's host tensor holds its ranges back to back."""
+    from cuasr_b200.host_pipeline import share_ranges
+    for elems, pieces, world in ((8192 * 8192, 4, 8), (1024 * 640, 4, 2), (4096, 1, 4), (96, 4, 3)):
+        covered = np.zeros(elems, dtype=np.int32)
+        for rank in range(world):
+            ranges = share_ranges(elems, pieces, rank, world)
+            assert len(ranges) == pieces
+            assert all(b - a == elems // (pieces * world) for a, b in ranges)
+            # piece p of this rank lies inside piece p of the operand
+            assert all(p * (elems // pieces) <= a and b <= (p + 1) * (elems // pieces) for p, (a, b) in enumerate(ranges))
+            for a, b in ranges:
+                covered[a:b] += 1
+        assert (covered == 1).all()
+    with pytest.raises(ValueError):
+        share_ranges(100, 4, 0, 3)
