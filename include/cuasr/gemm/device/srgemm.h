@@ -155,13 +155,28 @@ class Srgemm {
     return cuasr_b200_srgemm_workspace_size(&d, &a);
   }
 
-  cutlass::Status initialize(Arguments const& args, void* workspace = nullptr, cudaStream_t stream = nullptr) {
+  // Not in the reference: bytes of an OPTIONAL workspace that makes an unsplit launch faster (balanced last wave,
+  // packed adds on re-packed operands, unaligned operands kept on the fast kernel); 0 = nothing to gain.  Pass the
+  // buffer and its size to initialize() / operator() through their last parameter.  Needs a current device.
+  static size_t get_optional_workspace_size(Arguments const& args) {
     cuasr_b200_desc_t d = desc();
-    cuasr_b200_args_t a = pack(args, workspace, get_workspace_size(args), stream);
+    cuasr_b200_args_t a = pack(args, nullptr, 0, nullptr);
+    if (user_functors()) return 0;
+    return cuasr_b200_srgemm_optional_workspace_size(&d, &a);
+  }
+
+  // workspace_bytes: size of `workspace` when it is larger than get_workspace_size() asks for (the optional
+  // workspace above); 0 = exactly the required size, as in the reference.
+  cutlass::Status initialize(Arguments const& args, void* workspace = nullptr, cudaStream_t stream = nullptr,
+                             size_t workspace_bytes = 0) {
+    cuasr_b200_desc_t d = desc();
+    const size_t required = get_workspace_size(args);
+    cuasr_b200_args_t a = pack(args, workspace, workspace_bytes > required ? workspace_bytes : required, stream);
     cutlass::Status st = user_functors() ? user_can_implement(a, SplitKSerial)
                                          : static_cast<cutlass::Status>(cuasr_b200_srgemm_can_implement(&d, &a));
     if (st != cutlass::Status::kSuccess) return st;
-    if (a.workspace_bytes > 0 && workspace == nullptr) return cutlass::Status::kErrorWorkspaceNull;
+    if (required > 0 && workspace == nullptr) return cutlass::Status::kErrorWorkspaceNull;
+    if (workspace == nullptr) a.workspace_bytes = 0;
     args_ = a;
     initialized_ = true;
     return cutlass::Status::kSuccess;
@@ -189,8 +204,9 @@ class Srgemm {
 
   cutlass::Status operator()(cudaStream_t stream = nullptr) { return run(stream); }
 
-  cutlass::Status operator()(Arguments const& args, void* workspace = nullptr, cudaStream_t stream = nullptr) {
-    cutlass::Status st = initialize(args, workspace, stream);
+  cutlass::Status operator()(Arguments const& args, void* workspace = nullptr, cudaStream_t stream = nullptr,
+                             size_t workspace_bytes = 0) {
+    cutlass::Status st = initialize(args, workspace, stream, workspace_bytes);
     return st == cutlass::Status::kSuccess ? run(stream) : st;
   }
 
