@@ -51,6 +51,40 @@ def test_static_scratch_matches_workspace_split_k(cuda_device):
     assert np.array_equal(want.cpu().numpy(), ref)
 
 
+def test_static_scratch_with_operands_the_fast_kernel_cannot_read(cuda_device):
+    """The same entry point when an operand has an odd leading dimension: the split runs on the any-alignment
+    kernel and its reduction kernel, partials in the static array, and must again equal the workspace entry point
+    (two calls in a row) and the host SRGEMM."""
+    import torch
+
+    rng = np.random.default_rng(43)
+    m, n, k, slices = 130, 200, 1027, 4
+    lda = k + 1                                           # row-major A with an odd leading dimension
+    A = rng.integers(-8, 9, size=m * lda).astype(np.float32)
+    B = rng.integers(-8, 9, size=k * n).astype(np.float32)
+    C = rng.integers(-8, 9, size=m * n).astype(np.float32)
+    dA, dB, dC = (torch.from_numpy(x).cuda() for x in (A, B, C))
+    op = SrgemmSplitKParallel(Op.MINIMUM, Op.PLUS, DType.F32, ROW, COL, ROW)
+
+    def arguments(dD):
+        return Arguments((m, n, k), (dA, lda), (dB, k), (dC, n), (dD, n), (0.0, 0.0), slices)
+
+    want = torch.zeros(m * n, device="cuda")
+    ws = torch.empty(op.get_workspace_size(arguments(want)), dtype=torch.uint8, device="cuda")
+    assert op(arguments(want), ws) == Status.kSuccess
+    torch.cuda.synchronize()
+    assert op.last_kernel() == "generic_splitk"
+    for attempt in range(2):
+        got = torch.full((m * n,), -1.0, device="cuda")
+        assert srgemm_splitk_static(op, arguments(got)) == Status.kSuccess
+        torch.cuda.synchronize()
+        assert op.last_kernel() == "generic_splitk"
+        assert torch.equal(got, want), f"call {attempt + 1} differs from the workspace split-K result"
+    assert device_status() == 0
+    ref = util.run_oracle("minimum_plus", DType.F32, (ROW, COL, ROW), (m, n, k), 0.0, A, lda, B, k, 0.0, C, n)
+    assert np.array_equal(want.cpu().numpy(), ref)
+
+
 def test_static_scratch_rejects_oversized_problems(cuda_device):
     import torch
 
