@@ -207,18 +207,20 @@ size_t splitk_bytes_for_pieces(const cuasr_b200_desc_t& desc, const cuasr_b200_a
   return ticket_bytes_for(args) + es * tile_count(args) * kTileM * kTileN * static_cast<size_t>(pieces);
 }
 
-// Explicit split-K: how many pieces each caller slice is cut into.  The reference launches exactly tiles x slices
-// CTAs (include/cuasr/gemm/kernel/srgemm_splitk_parallel.h:86-89), whatever the GPU; here a slice count that leaves
-// SMs idle (4 tiles x 16 slices = 64 work items on 148 SMs) is refined: every slice is cut into `sub` pieces of
-// consecutive K tiles, so the fold order stays slice-major, piece-minor.  That is only done where (+) is exact and
-// order-independent (everything but floating-point plus), so the result cannot depend on the SM count.  The cost
-// model counts K tiles: waves x (K tiles per piece) for the contraction, plus half a K tile per piece for parking
-// and folding a 128 x 128 partial.
+// Explicit split-K: into how many pieces of consecutive K tiles every output tile is really cut.  The reference
+// launches exactly tiles x slices CTAs (include/cuasr/gemm/kernel/srgemm_splitk_parallel.h:86-89), whatever the GPU;
+// here a slice count that leaves SMs idle (4 tiles x 16 slices = 64 work items on 148 SMs, or 4 x 32 = 128) is
+// refined to the piece count in [slices, 8 x slices] that the cost model likes best (4 x 37 = 148).  That is only
+// done where (+) is exact and order-independent (everything but floating-point plus): the pieces are folded in K
+// order and the result cannot depend on how K was cut, hence not on the SM count either.  The cost model counts K
+// tiles: waves x (K tiles per piece) for the contraction, plus half a K tile per piece for parking and folding a
+// 128 x 128 partial.
 bool splitk_order_independent(const cuasr_b200_desc_t& desc) {
   return !(desc.add_op == CUASR_OP_PLUS && (desc.dtype == CUASR_F32 || desc.dtype == CUASR_F64));
 }
-int splitk_sub_pieces(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int sms) {
-  if (sms <= 0 || args.split_k_slices <= 1 || !splitk_order_independent(desc)) return 1;
+long long splitk_pieces(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int sms, long long max_pieces) {
+  const long long slices = args.split_k_slices;
+  if (sms <= 0 || slices <= 1 || !splitk_order_independent(desc)) return slices;
   const int tk = kTileKBytes / (desc.dtype == CUASR_F64 ? 8 : 4);
   const long long k_tiles = (args.k + tk - 1) / tk;
   const long long tiles = static_cast<long long>(tile_count(args));
@@ -226,13 +228,12 @@ int splitk_sub_pieces(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& ar
     const long long waves = (tiles * pieces + sms - 1) / sms;
     return static_cast<double>(waves * ((k_tiles + pieces - 1) / pieces)) + 0.5 * static_cast<double>(pieces);
   };
-  int best = 1;
-  double best_cost = cost(args.split_k_slices);
-  for (int sub = 2; sub <= 8; ++sub) {
-    const long long pieces = static_cast<long long>(args.split_k_slices) * sub;
-    if (pieces * 4 > k_tiles) break;                      // keep at least four K tiles per piece
+  long long best = slices;
+  double best_cost = cost(slices);
+  const long long limit = std::min<long long>(std::min<long long>(8 * slices, max_pieces), k_tiles / 4);
+  for (long long pieces = slices + 1; pieces <= limit; ++pieces) {
     const double c = cost(pieces);
-    if (c < 0.95 * best_cost) { best = sub; best_cost = c; }
+    if (c < 0.97 * best_cost) { best = pieces; best_cost = c; }
   }
   return best;
 }
@@ -247,8 +248,8 @@ size_t splitk_workspace_bytes(const cuasr_b200_desc_t& desc, const cuasr_b200_ar
 size_t splitk_workspace_bytes_refined(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args) {
   if (args.split_k_slices <= 1) return 0;
   DeviceState* dev = nullptr;
-  const int sub = device_state(&dev) ? splitk_sub_pieces(desc, args, dev->sms) : 1;
-  return splitk_bytes_for_pieces(desc, args, static_cast<long long>(args.split_k_slices) * sub);
+  const long long pieces = device_state(&dev) ? splitk_pieces(desc, args, dev->sms, 1LL << 30) : args.split_k_slices;
+  return splitk_bytes_for_pieces(desc, args, pieces);
 }
 
 // Load balancing of a launch that was not asked to split K: the tiles of the last, partial wave are cut along K
@@ -402,9 +403,10 @@ int run_typed(const cuasr_b200_desc_t& desc, const cuasr_b200_args_t& args, int 
     if (args.workspace == nullptr) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
     if (args.workspace_bytes < need) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
     if (!workspace_aligned) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
-    int sub = splitk_sub_pieces(desc, args, dev->sms);
-    while (sub > 1 && args.workspace_bytes < splitk_bytes_for_pieces(desc, args, static_cast<long long>(slices) * sub)) --sub;
-    plan = BalancePlan{0, slices * sub};
+    // as many pieces as the workspace at hand has room for (it always has room for `slices`)
+    const size_t per_piece = splitk_bytes_for_pieces(desc, args, 1) - splitk_bytes_for_pieces(desc, args, 0);
+    const long long room = static_cast<long long>((args.workspace_bytes - splitk_bytes_for_pieces(desc, args, 0)) / per_piece);
+    plan = BalancePlan{0, static_cast<int>(splitk_pieces(desc, args, dev->sms, room))};
   } else if (args.workspace != nullptr && workspace_aligned) {
     // an optional workspace on an unsplit launch buys load balancing, if it is large enough for the plan
     constexpr int tk = kTileKBytes / sizeof(T);

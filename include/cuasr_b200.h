@@ -124,10 +124,11 @@ CUASR_B200_API int cuasr_b200_srgemm_path(const cuasr_b200_desc_t *desc, const c
  * (device/srgemm_splitk_parallel.h:220-235, :238-279, :333-348).  The reference needs
  * sizeof(element) * M * N * slices bytes of workspace and two launches; this library needs a little more
  * (per-tile arrival counters) and one launch: the CTA that completes a tile last combines the slices
- * in slice order and applies the epilogue.  Where the slice count leaves SMs idle (tiles x slices below or badly
- * off a multiple of the SM count) and (+) is exact and order-independent (everything but floating-point plus), every
- * slice is cut into up to 8 pieces of consecutive K; the workspace size reported with a current device has room
- * for that, a workspace of only the reference's size is accepted and limits the cutting. */
+ * in K order and applies the epilogue.  Where the slice count leaves SMs idle (tiles x slices below or badly
+ * off a multiple of the SM count) and (+) is exact and order-independent (everything but floating-point plus), K is
+ * cut into more pieces than asked, up to 8 x slices (256 x 256 outputs on 148 SMs: 37 pieces per tile whether 16 or
+ * 32 slices were asked for); the result does not depend on the cutting.  The workspace size reported with a current
+ * device has room for that; a workspace of only the reference's size is accepted and limits the cutting. */
 CUASR_B200_API int cuasr_b200_srgemm_splitk_can_implement(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 CUASR_B200_API size_t cuasr_b200_srgemm_splitk_workspace_size(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 CUASR_B200_API int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
