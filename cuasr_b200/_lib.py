@@ -60,7 +60,8 @@ class ApspShardArgs(ctypes.Structure):     # cuasr_b200_apsp_shard_args_t
 
 class ApspMultiArgs(ctypes.Structure):     # cuasr_b200_apsp_multi_args_t
     _fields_ = [
-        ("dtype", ctypes.c_int32), ("n", ctypes.c_int32), ("iterations", ctypes.c_int32), ("n_devices", ctypes.c_int32),
+        ("dtype", ctypes.c_int32), ("algorithm", ctypes.c_int32), ("n", ctypes.c_int32), ("block", ctypes.c_int32),
+        ("iterations", ctypes.c_int32), ("n_devices", ctypes.c_int32),
         ("devices", ctypes.POINTER(ctypes.c_int32)),
         ("buf0", ctypes.POINTER(ctypes.c_void_p)), ("buf1", ctypes.POINTER(ctypes.c_void_p)),
         ("ldd", ctypes.c_int64),
@@ -88,6 +89,7 @@ PROTOTYPES = {
     "cuasr_b200_apsp": (ctypes.c_int, [ctypes.POINTER(ApspArgs)]),
     "cuasr_b200_apsp_shard_squaring": (ctypes.c_int, [ctypes.POINTER(ApspShardArgs)]),
     "cuasr_b200_apsp_multi": (ctypes.c_int, [ctypes.POINTER(ApspMultiArgs)]),
+    "cuasr_b200_apsp_multi_workspace_size": (ctypes.c_size_t, [ctypes.POINTER(ApspMultiArgs)]),
     "cuasr_b200_apsp_multi_partition": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
                                                        ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
     "cuasr_b200_flag_raise": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_uint32,

@@ -441,27 +441,47 @@ def multi_partition(n: int, n_devices: int, g: int):
     return (col0.value, cols.value) if st == 0 else None
 
 
-def multi_device_solve(dtype: DType, n: int, devices: Sequence[int], buf0: Sequence[int], buf1: Sequence[int],
+def multi_device_workspace_size(dtype: DType, n: int, n_devices: int, algorithm: int = BLOCKED_FLOYD_WARSHALL,
+                                block: int = 0) -> int:
+    """cuasr_b200_apsp_multi_workspace_size: bytes of scratch every GPU needs (0 for repeated squaring, whose
+    workspace is optional, and for arguments the solve would refuse)."""
+    import ctypes
+
+    from . import _lib
+
+    a = _lib.ApspMultiArgs()
+    a.dtype, a.algorithm, a.n, a.block, a.n_devices, a.ldd = int(dtype), int(algorithm), int(n), int(block), int(n_devices), int(n)
+    return int(_lib.load().cuasr_b200_apsp_multi_workspace_size(ctypes.byref(a)))
+
+
+def multi_device_solve(dtype: DType, n: int, devices: Sequence[int], buf0: Sequence[int], buf1: Sequence[int] = (),
                        ldd: Optional[int] = None, iterations: int = 0, workspaces: Sequence[int] = (),
-                       workspace_bytes: int = 0, streams: Sequence[int] = ()):
-    """cuasr_b200_apsp_multi on device addresses: the sharded repeated-squaring solve on the GPUs `devices` of this
-    machine from one process (one host thread per GPU inside the library, peer stores between the GPUs).  buf0[g]
-    must hold the whole distance matrix on every GPU.  Returns (Status, index of the buffer that holds the result,
-    list of per-GPU device status words).  Blocks until the solve is done."""
+                       workspace_bytes: int = 0, streams: Sequence[int] = (), algorithm: int = REPEATED_SQUARING,
+                       block: int = 0):
+    """cuasr_b200_apsp_multi on device addresses: the sharded solve on the GPUs `devices` of this machine from one
+    process (one host thread per GPU inside the library, peer stores between the GPUs).
+    Repeated squaring: buf0[g] holds the whole distance matrix on every GPU, buf1[g] is a second matrix.
+    Blocked Floyd-Warshall: buf0[g] holds the column blocks g, g + G, ... of `block` vertices (n x n/G, leading
+    dimension ldd), buf1 is not used and `workspaces` (multi_device_workspace_size bytes each) are required.
+    Returns (Status, index of the buffer that holds the result, list of per-GPU device status words).  Blocks until
+    the solve is done."""
     import ctypes
 
     from . import _lib
 
     G = len(devices)
     a = _lib.ApspMultiArgs()
-    a.dtype, a.n, a.iterations, a.n_devices = int(dtype), int(n), int(iterations), G
+    a.dtype, a.algorithm, a.n, a.block, a.iterations, a.n_devices = int(dtype), int(algorithm), int(n), int(block), int(iterations), G
     dev_arr = (ctypes.c_int32 * max(G, 1))(*[int(d) for d in devices])
     b0 = (ctypes.c_void_p * max(G, 1))(*[int(p) or None for p in buf0])
-    b1 = (ctypes.c_void_p * max(G, 1))(*[int(p) or None for p in buf1])
     a.devices = ctypes.cast(dev_arr, ctypes.POINTER(ctypes.c_int32))
-    a.buf0, a.buf1 = ctypes.cast(b0, ctypes.POINTER(ctypes.c_void_p)), ctypes.cast(b1, ctypes.POINTER(ctypes.c_void_p))
+    a.buf0 = ctypes.cast(b0, ctypes.POINTER(ctypes.c_void_p))
     a.ldd = int(n if ldd is None else ldd)
-    keep = [dev_arr, b0, b1]
+    keep = [dev_arr, b0]
+    if buf1:
+        b1 = (ctypes.c_void_p * max(G, 1))(*[int(p) or None for p in buf1])
+        a.buf1 = ctypes.cast(b1, ctypes.POINTER(ctypes.c_void_p))
+        keep.append(b1)
     if workspaces:
         ws = (ctypes.c_void_p * G)(*[int(p) or None for p in workspaces])
         a.workspace, a.workspace_bytes = ctypes.cast(ws, ctypes.POINTER(ctypes.c_void_p)), int(workspace_bytes)

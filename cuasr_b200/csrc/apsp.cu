@@ -247,17 +247,58 @@ int cuasr_b200_apsp_multi_partition(int32_t n, int32_t n_devices, int32_t g, int
   return CUASR_STATUS_SUCCESS;
 }
 
+namespace {
+constexpr int kDefaultMultiBlock = 512;
+int multi_block(const cuasr_b200_apsp_multi_args_t& a) { return a.block > 0 ? a.block : kDefaultMultiBlock; }
+bool multi_valid(const cuasr_b200_apsp_multi_args_t* a) {
+  if (a == nullptr || (a->dtype != CUASR_F32 && a->dtype != CUASR_F64)) return false;
+  if (a->algorithm != CUASR_APSP_REPEATED_SQUARING && a->algorithm != CUASR_APSP_BLOCKED_FLOYD_WARSHALL) return false;
+  if (a->n <= 0 || a->n_devices < 1 || a->n_devices > 8 || a->n % a->n_devices != 0 || a->ldd < a->n) return false;
+  if (a->iterations < 0 || a->block < 0 || a->block % 4 != 0) return false;
+  if (a->algorithm == CUASR_APSP_BLOCKED_FLOYD_WARSHALL &&
+      a->n % (static_cast<long long>(a->n_devices) * multi_block(*a)) != 0)
+    return false;
+  return true;
+}
+// Per-GPU scratch of the sharded Floyd-Warshall solve, as offsets into the workspace.
+constexpr int kPanelBuffers = 3;
+struct MultiFwLayout {
+  size_t p_col[kPanelBuffers], p_row, diag[2], total;
+};
+MultiFwLayout multi_fw_layout(const cuasr_b200_apsp_multi_args_t& a) {
+  const size_t es = elem_size(a.dtype), n = a.n, b = multi_block(a), cols = n / a.n_devices;
+  MultiFwLayout l;
+  size_t off = 0;
+  for (int i = 0; i < kPanelBuffers; ++i) { l.p_col[i] = off; off = align_up(off + n * b * es, 256); }
+  l.p_row = off; off = align_up(off + b * cols * es, 256);
+  for (int i = 0; i < 2; ++i) { l.diag[i] = off; off = align_up(off + b * b * es, 256); }
+  l.total = off;
+  return l;
+}
+}  // namespace
+
+size_t cuasr_b200_apsp_multi_workspace_size(const cuasr_b200_apsp_multi_args_t* a) {
+  if (!multi_valid(a) || a->algorithm != CUASR_APSP_BLOCKED_FLOYD_WARSHALL) return 0;
+  return multi_fw_layout(*a).total;
+}
+
 int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
-  if (a == nullptr || (a->dtype != CUASR_F32 && a->dtype != CUASR_F64)) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
-  if (a->n <= 0 || a->n_devices < 1 || a->n_devices > 8 || a->n % a->n_devices != 0 || a->ldd < a->n)
-    return CUASR_STATUS_ERROR_INVALID_PROBLEM;
-  if (a->devices == nullptr || a->buf0 == nullptr || a->buf1 == nullptr || a->result_buffer == nullptr)
+  if (!multi_valid(a)) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  const bool fw = a->algorithm == CUASR_APSP_BLOCKED_FLOYD_WARSHALL;
+  if (a->devices == nullptr || a->buf0 == nullptr || (!fw && a->buf1 == nullptr) || a->result_buffer == nullptr)
     return CUASR_STATUS_ERROR_INVALID_PROBLEM;
   const int G = a->n_devices;
   for (int g = 0; g < G; ++g) {
-    if (a->buf0[g] == nullptr || a->buf1[g] == nullptr) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+    if (a->buf0[g] == nullptr || (!fw && a->buf1[g] == nullptr)) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
     for (int h = 0; h < g; ++h)
       if (a->devices[g] == a->devices[h]) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  }
+  if (fw) {
+    if (a->workspace == nullptr || a->workspace_bytes < multi_fw_layout(*a).total) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
+    for (int g = 0; g < G; ++g) {
+      if (a->workspace[g] == nullptr) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
+      if (reinterpret_cast<uintptr_t>(a->workspace[g]) % 256 != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+    }
   }
   const int steps = a->iterations > 0 ? a->iterations : std::max(1, ceil_log2(a->n));
 
@@ -288,27 +329,11 @@ int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
   } barrier(G, failed);
   auto fail = [&](int status) { int expected = CUASR_STATUS_SUCCESS; failed.compare_exchange_strong(expected, status); };
 
-  auto worker = [&](int g) {
-    bool ok = cudaSetDevice(a->devices[g]) == cudaSuccess;
-    if (!ok) fail(CUASR_STATUS_ERROR_INTERNAL);
-    for (int h = 0; ok && h < G; ++h) {
-      if (h == g) continue;
-      int can = 0;
-      if (cudaDeviceCanAccessPeer(&can, a->devices[g], a->devices[h]) != cudaSuccess || !can) {
-        fail(CUASR_STATUS_ERROR_NOT_SUPPORTED);
-        ok = false;
-        break;
-      }
-      const cudaError_t e = cudaDeviceEnablePeerAccess(a->devices[h], 0);
-      if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
-      else if (e != cudaSuccess) { fail(CUASR_STATUS_ERROR_INTERNAL); ok = false; }
-    }
-    cudaStream_t stream = a->streams != nullptr ? static_cast<cudaStream_t>(a->streams[g]) : nullptr;
+  // one squaring per step: every GPU computes its block of columns and stores it into every GPU's next iterate
+  auto squaring_steps = [&](int g, cudaStream_t stream) {
     int32_t col0 = 0, cols = 0;
     cuasr_b200_apsp_multi_partition(a->n, G, g, &col0, &cols);
-    // every GPU has its peers mapped, or somebody failed
-    const bool run = barrier.arrive_and_wait() == CUASR_STATUS_SUCCESS;
-    for (int s = 0; run && s < steps; ++s) {
+    for (int s = 0; s < steps; ++s) {
       void* const* cur = (s % 2 == 0) ? a->buf0 : a->buf1;
       void* const* nxt = (s % 2 == 0) ? a->buf1 : a->buf0;
       void* peers[7];
@@ -330,6 +355,113 @@ int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
       if (cudaStreamSynchronize(stream) != cudaSuccess) fail(CUASR_STATUS_ERROR_INTERNAL);
       if (barrier.arrive_and_wait() != CUASR_STATUS_SUCCESS) break;   // the same answer on every thread
     }
+  };
+
+  // Blocked Floyd-Warshall, one block of vertices per step, with the column panel of the NEXT step computed first:
+  // in step kb the owner of block kb + 1 brings that block up to date, closes its diagonal block, computes the
+  // column panel and stores it into every GPU's panel buffer (kb + 1) % 3, and only then updates the rest of its
+  // columns, so the other GPUs find the panel waiting when they finish step kb.
+  // Who waits for what, on the host: before the barrier of step kb every thread waits until its own GPU has
+  // finished step kb - 2, and the owner of block kb until its panel has been stored everywhere.  After the barrier,
+  // then, panel kb is complete on every GPU, and the buffer the owner of block kb + 1 is about to fill (it last held
+  // panel kb - 2, read in step kb - 2) has no reader left.  The GPUs always have a step queued ahead.
+  auto floyd_warshall_steps = [&](int g, cudaStream_t stream) {
+    const cuasr_b200_desc_t desc = minplus_desc(a->dtype);
+    const size_t es = elem_size(a->dtype);
+    const int n = a->n, b = multi_block(*a), cols = n / G, blocks = n / b;
+    const MultiFwLayout l = multi_fw_layout(*a);
+    char* ws = static_cast<char*>(a->workspace[g]);
+    char* D = static_cast<char*>(a->buf0[g]);
+    void* p_row = ws + l.p_row;                               // b x cols, leading dimension b
+    void* diag[2] = {ws + l.diag[0], ws + l.diag[1]};         // b x b
+    cudaEvent_t done[kPanelBuffers] = {}, pushed = nullptr;
+    bool events = cudaEventCreateWithFlags(&pushed, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < kPanelBuffers; ++i)
+      events = events && cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!events) fail(CUASR_STATUS_ERROR_INTERNAL);
+    auto product = [&](int m, int nn, int k, const void* A, long long lda, const void* B, long long ldb, const void* C,
+                       long long ldc, void* out, long long ldo, int n_extra, void* const* extra) {
+      cuasr_b200_args_t s = minplus_args(a->dtype, m, nn, k, A, lda, B, ldb, C, ldc, out, ldo, nullptr, 0, stream);
+      return n_extra > 0 ? cuasr_b200_srgemm_push(&desc, &s, n_extra, extra) : cuasr_b200_srgemm(&desc, &s);
+    };
+    // phases 1 and 2 (column part) of block kb, by its owner: the closed diagonal block from a private copy, then
+    // P_col = min(D[:, K], D[:, K] (x) D[K, K]*) into every GPU's panel buffer; `pushed` marks the end of it
+    auto make_panel = [&](int kb) {
+      const int k0 = kb * b;
+      char* panel = D + static_cast<size_t>(kb / G) * b * a->ldd * es;      // my columns of block kb
+      if (cudaMemcpy2DAsync(diag[0], b * es, panel + static_cast<size_t>(k0) * es, a->ldd * es, b * es, b,
+                            cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+        return static_cast<int>(CUASR_STATUS_ERROR_INTERNAL);
+      int cur = 0, st = CUASR_STATUS_SUCCESS;
+      for (int it = 0; st == CUASR_STATUS_SUCCESS && it < std::max(1, ceil_log2(b)); ++it, cur = 1 - cur)
+        st = product(b, b, b, diag[cur], b, diag[cur], b, diag[cur], b, diag[1 - cur], b, 0, nullptr);
+      if (st != CUASR_STATUS_SUCCESS) return st;
+      void* peers[7];
+      int np = 0;
+      for (int h = 0; h < G; ++h)
+        if (h != g) peers[np++] = static_cast<char*>(a->workspace[h]) + l.p_col[kb % kPanelBuffers];
+      st = product(n, b, b, panel, a->ldd, diag[cur], b, panel, a->ldd, ws + l.p_col[kb % kPanelBuffers], n, np, peers);
+      if (st == CUASR_STATUS_SUCCESS && cudaEventRecord(pushed, stream) != cudaSuccess) st = CUASR_STATUS_ERROR_INTERNAL;
+      return st;
+    };
+    bool wait_for_push = false;
+    if (events && g == 0) {                                   // block 0 has no step before it
+      const int st = make_panel(0);
+      if (st != CUASR_STATUS_SUCCESS) fail(st);
+      wait_for_push = true;
+    }
+    for (int kb = 0; kb < blocks; ++kb) {    // without events the status is a failure already: everybody leaves at the first barrier
+      if (wait_for_push && cudaEventSynchronize(pushed) != cudaSuccess) fail(CUASR_STATUS_ERROR_INTERNAL);
+      wait_for_push = false;
+      if (kb >= 2 && cudaEventSynchronize(done[(kb - 2) % kPanelBuffers]) != cudaSuccess) fail(CUASR_STATUS_ERROR_INTERNAL);
+      if (barrier.arrive_and_wait() != CUASR_STATUS_SUCCESS) break;
+      const int k0 = kb * b;
+      const char* p_col = ws + l.p_col[kb % kPanelBuffers];   // n x b, leading dimension n; rows K of it = D[K, K]*
+      // phase 2, my piece of the row panel: P_row = min(D[K, mine], D[K, K]* (x) D[K, mine])
+      const char* rows = D + static_cast<size_t>(k0) * es;
+      int st = product(b, cols, b, p_col + static_cast<size_t>(k0) * es, n, rows, a->ldd, rows, a->ldd, p_row, b, 0, nullptr);
+      if (st == CUASR_STATUS_SUCCESS && kb + 1 < blocks && (kb + 1) % G == g) {
+        // the next block is mine: phase 3 on it alone, then its panel goes out before the rest of phase 3
+        const size_t lc = static_cast<size_t>((kb + 1) / G) * b;
+        char* blk = D + lc * a->ldd * es;
+        st = product(n, b, b, p_col, n, static_cast<char*>(p_row) + lc * b * es, b, blk, a->ldd, blk, a->ldd, 0, nullptr);
+        if (st == CUASR_STATUS_SUCCESS) st = make_panel(kb + 1);
+        wait_for_push = true;
+      }
+      // phase 3: my columns through the two panels, in place (the operands are copies).  A block that was brought
+      // up to date above is simply visited again: min(D, P_col (x) P_row) changes nothing the second time.
+      if (st == CUASR_STATUS_SUCCESS) st = product(n, cols, b, p_col, n, p_row, b, D, a->ldd, D, a->ldd, 0, nullptr);
+      if (st == CUASR_STATUS_SUCCESS && cudaEventRecord(done[kb % kPanelBuffers], stream) != cudaSuccess)
+        st = CUASR_STATUS_ERROR_INTERNAL;
+      if (st != CUASR_STATUS_SUCCESS) fail(st);
+    }
+    if (cudaStreamSynchronize(stream) != cudaSuccess) fail(CUASR_STATUS_ERROR_INTERNAL);
+    if (pushed != nullptr) cudaEventDestroy(pushed);
+    for (int i = 0; i < kPanelBuffers; ++i)
+      if (done[i] != nullptr) cudaEventDestroy(done[i]);
+  };
+
+  auto worker = [&](int g) {
+    bool ok = cudaSetDevice(a->devices[g]) == cudaSuccess;
+    if (!ok) fail(CUASR_STATUS_ERROR_INTERNAL);
+    for (int h = 0; ok && h < G; ++h) {
+      if (h == g) continue;
+      int can = 0;
+      if (cudaDeviceCanAccessPeer(&can, a->devices[g], a->devices[h]) != cudaSuccess || !can) {
+        fail(CUASR_STATUS_ERROR_NOT_SUPPORTED);
+        ok = false;
+        break;
+      }
+      const cudaError_t e = cudaDeviceEnablePeerAccess(a->devices[h], 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+      else if (e != cudaSuccess) { fail(CUASR_STATUS_ERROR_INTERNAL); ok = false; }
+    }
+    cudaStream_t stream = a->streams != nullptr ? static_cast<cudaStream_t>(a->streams[g]) : nullptr;
+    // every GPU has its peers mapped, or somebody failed
+    if (barrier.arrive_and_wait() == CUASR_STATUS_SUCCESS) {
+      if (fw) floyd_warshall_steps(g, stream);
+      else squaring_steps(g, stream);
+    }
     if (a->device_status != nullptr) a->device_status[g] = cuasr_b200_device_status(stream);
   };
 
@@ -337,7 +469,7 @@ int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
   threads.reserve(G);
   for (int g = 0; g < G; ++g) threads.emplace_back(worker, g);
   for (auto& t : threads) t.join();
-  *a->result_buffer = steps % 2;
+  *a->result_buffer = fw ? 0 : steps % 2;
   return failed.load();
 }
 

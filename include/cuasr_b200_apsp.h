@@ -73,33 +73,44 @@ typedef struct cuasr_b200_apsp_shard_args {
 
 CUASR_B200_API int cuasr_b200_apsp_shard_squaring(const cuasr_b200_apsp_shard_args_t *args);
 
-/* The whole sharded solve by repeated squaring on the GPUs of one machine, from one host process: one host thread
- * per GPU, plain peer access between the GPUs (no other library), each squaring one
- * cuasr_b200_apsp_shard_squaring per GPU whose epilogue stores the GPU's block of columns into every GPU's next
- * iterate, then a barrier of the host threads (each synchronises its own stream first).  Every tensor map a kernel
- * reads through describes memory of the GPU that runs it; only plain stores cross NVLink.
+/* The whole sharded solve on the GPUs of one machine, from one host process: one host thread per GPU, plain peer
+ * access between the GPUs (no other library), the push epilogue of the SRGEMM as the only exchange, and a barrier of
+ * the host threads between steps (each waits for its own GPU's part first; the barrier also makes the threads agree
+ * on the status, so a failure on one GPU stops all of them at the same step).  Every tensor map a kernel reads
+ * through describes memory of the GPU that runs it; only plain stores cross NVLink.
  *
- * The caller owns all memory.  For each of the n_devices (1..8) GPUs, in the order of `devices`:
- *   buf0[g], buf1[g]   two n x n matrices on device devices[g] (leading dimension ldd, the same everywhere);
- *                      before the call buf0[g] holds the whole distance matrix on EVERY GPU (the call copies nothing
- *                      between GPUs but the results of the squarings);
- *   workspace[g]       optional per-GPU scratch of workspace_bytes (may be NULL; load balance only);
- *   streams[g]         a stream of device devices[g], or NULL for its default stream.
- * Columns are dealt out in contiguous blocks of n / n_devices (n must divide).  On return every GPU has finished
- * and holds the complete closure in buf0[g] or buf1[g]; *result_buffer says which (0 or 1).  The call blocks the
- * calling host thread until the solve is done.  Status: CUASR_STATUS_ERROR_NOT_SUPPORTED when a GPU cannot reach a
- * peer's memory, otherwise the first error any GPU met; `device_status` (n_devices entries, may be NULL) receives
- * each GPU's cuasr_b200_device_status after the solve. */
+ * The caller owns all memory.  n_devices is 1..8, `devices` their CUDA ordinals; per GPU g, in that order:
+ *   streams[g]         a stream of device devices[g], or NULL for its default stream;
+ *   workspace[g]       device scratch of workspace_bytes.
+ * CUASR_APSP_REPEATED_SQUARING (n divisible by n_devices): GPU g owns the contiguous columns
+ *   [g n / G, (g + 1) n / G) (cuasr_b200_apsp_multi_partition).  buf0[g] and buf1[g] are two n x n matrices
+ *   (leading dimension ldd) on GPU g; before the call buf0[g] holds the whole distance matrix on EVERY GPU.  Each
+ *   squaring is one cuasr_b200_apsp_shard_squaring per GPU, which stores the GPU's block into every GPU's next
+ *   iterate.  On return every GPU holds the complete closure in buf0[g] or buf1[g]; *result_buffer says which.
+ *   The workspace is optional here (load balance; may be NULL).
+ * CUASR_APSP_BLOCKED_FLOYD_WARSHALL (n divisible by n_devices x block): the column blocks of `block` vertices are
+ *   dealt out cyclically, GPU g owns blocks g, g + G, g + 2 G, ... and buf0[g] holds exactly those columns, one
+ *   block after the other, as an n x (n / G) matrix with leading dimension ldd >= n; buf1 is not used.  Per block
+ *   the owner closes the diagonal block, computes the column panel and stores it into every GPU's panel buffer
+ *   (one step ahead: the owner of the next block does this before the bulk of its own update, so the panel is
+ *   waiting when the others get there); every GPU updates its piece of the row panel and its own columns in
+ *   place.  The closure ends up in buf0 (*result_buffer = 0), distributed as it came.  The workspace is REQUIRED:
+ *   cuasr_b200_apsp_multi_workspace_size bytes per GPU, 256-byte aligned.
+ * The call blocks the calling host thread until the solve is done.  Status: CUASR_STATUS_ERROR_NOT_SUPPORTED when a
+ * GPU cannot reach a peer's memory, otherwise the first error any GPU met; `device_status` (n_devices entries, may
+ * be NULL) receives each GPU's cuasr_b200_device_status after the solve. */
 typedef struct cuasr_b200_apsp_multi_args {
   int32_t dtype;            /* CUASR_F32 or CUASR_F64 */
+  int32_t algorithm;        /* cuasr_apsp_algorithm_t */
   int32_t n;
-  int32_t iterations;       /* squarings; 0 = ceil(log2 n) */
+  int32_t block;            /* Floyd-Warshall block size, a multiple of 4; 0 = 512 */
+  int32_t iterations;       /* repeated squaring: squarings; 0 = ceil(log2 n) */
   int32_t n_devices;
   const int32_t *devices;   /* CUDA device ordinals */
   void *const *buf0;
-  void *const *buf1;
+  void *const *buf1;        /* repeated squaring only */
   int64_t ldd;
-  void *const *workspace;   /* NULL, or n_devices entries each NULL or a device pointer */
+  void *const *workspace;   /* n_devices entries (repeated squaring: NULL, or entries that may be NULL) */
   size_t workspace_bytes;
   void *const *streams;     /* NULL, or n_devices entries */
   int32_t *result_buffer;   /* out */
@@ -108,8 +119,13 @@ typedef struct cuasr_b200_apsp_multi_args {
 
 CUASR_B200_API int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t *args);
 
-/* How the columns are dealt out by cuasr_b200_apsp_multi: first column and number of columns of GPU `g` of
- * `n_devices`.  Returns 0, or CUASR_STATUS_ERROR_INVALID_PROBLEM when n does not divide or an index is out of range. */
+/* Bytes of per-GPU scratch cuasr_b200_apsp_multi needs (0 for repeated squaring, whose workspace is optional, and
+ * for invalid arguments): three column panels, one row-panel piece and two diagonal blocks for Floyd-Warshall. */
+CUASR_B200_API size_t cuasr_b200_apsp_multi_workspace_size(const cuasr_b200_apsp_multi_args_t *args);
+
+/* How the columns are dealt out by the repeated-squaring form of cuasr_b200_apsp_multi: first column and number of
+ * columns of GPU `g` of `n_devices`.  Returns 0, or CUASR_STATUS_ERROR_INVALID_PROBLEM when n does not divide or an
+ * index is out of range. */
 CUASR_B200_API int cuasr_b200_apsp_multi_partition(int32_t n, int32_t n_devices, int32_t g, int32_t *col0, int32_t *cols);
 
 /* One-sided ordering between GPUs, for solves in which one rank produces what the others consume (the column

@@ -57,6 +57,61 @@ def test_multi_gpu_entry_point_partition_and_argument_checks():
     assert st == Status.kErrorInvalidProblem                 # not a distance type
     st, _, _ = apsp.multi_device_solve(DType.F32, 1024, [0], [4096], [8192], ldd=1000)
     assert st == Status.kErrorInvalidProblem
+    # the Floyd-Warshall form: whole blocks per GPU, and a workspace on every GPU
+    fw = dict(algorithm=apsp.BLOCKED_FLOYD_WARSHALL, block=256)
+    need = apsp.multi_device_workspace_size(DType.F32, 4096, 2, block=512)
+    assert need == 4 * (3 * 4096 * 512 + 512 * 2048 + 2 * 512 * 512)      # three column panels, a row piece, two blocks
+    assert apsp.multi_device_workspace_size(DType.F32, 4096, 3) == 0
+    assert apsp.multi_device_workspace_size(DType.F32, 4096, 2, apsp.REPEATED_SQUARING) == 0
+    st, _, _ = apsp.multi_device_solve(DType.F32, 1024, [0, 1], [4096] * 2, **fw)
+    assert st == Status.kErrorWorkspaceNull
+    st, _, _ = apsp.multi_device_solve(DType.F32, 1024, [0, 1], [4096] * 2, workspaces=[4096] * 2, workspace_bytes=100, **fw)
+    assert st == Status.kErrorWorkspaceNull
+    st, _, _ = apsp.multi_device_solve(DType.F32, 1024, [0, 1], [4096] * 2, workspaces=[4096, 4100], workspace_bytes=1 << 30, **fw)
+    assert st == Status.kErrorMisalignedOperand
+    st, _, _ = apsp.multi_device_solve(DType.F32, 1024, [0, 1], [4096] * 2, workspaces=[4096] * 2, workspace_bytes=1 << 30,
+                                       algorithm=apsp.BLOCKED_FLOYD_WARSHALL, block=384)     # 1024 % (2 x 384)
+    assert st == Status.kErrorInvalidProblem
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,block,pad,dt", [(1024, 128, 0, DType.F32), (1536, 256, 8, DType.F32), (768, 64, 0, DType.F64)])
+def test_multi_gpu_floyd_warshall_from_one_process(cuda_device, n, block, pad, dt):
+    """cuasr_b200_apsp_multi, blocked Floyd-Warshall: column blocks dealt out cyclically over the GPUs of the box
+    (one GPU included), the column panel of every step stored into every GPU's panel buffer by the owner's
+    epilogue; the distributed closure, put together again, must equal the host's."""
+    import torch
+    np_t, t_t = (np.float32, torch.float32) if dt == DType.F32 else (np.float64, torch.float64)
+    w = _graph(n, n + block, np_t)
+    want = _closure(w)
+    G = min(torch.cuda.device_count(), 4)
+    while n % (G * block):
+        G -= 1
+    ld, cols, blocks = n + pad, n // G, n // block
+    owned = [[kb for kb in range(blocks) if kb % G == g] for g in range(G)]
+    bufs = []
+    for g in range(G):
+        buf = np.full((cols, ld), 7.0, dtype=np_t)               # column c of the piece is row c of this array
+        for i, kb in enumerate(owned[g]):
+            buf[i * block:(i + 1) * block, :n] = w[:, kb * block:(kb + 1) * block].T
+        bufs.append(torch.from_numpy(buf).to(f"cuda:{g}"))
+    need = apsp.multi_device_workspace_size(dt, n, G, block=block)
+    assert need > 0
+    ws = [torch.empty(need, dtype=torch.uint8, device=f"cuda:{g}") for g in range(G)]
+    for g in range(G):
+        torch.cuda.synchronize(g)
+    st, which, status = apsp.multi_device_solve(dt, n, list(range(G)), [t.data_ptr() for t in bufs], ldd=ld,
+                                                workspaces=[t.data_ptr() for t in ws], workspace_bytes=need,
+                                                algorithm=apsp.BLOCKED_FLOYD_WARSHALL, block=block)
+    assert st == Status.kSuccess and which == 0 and status == [0] * G
+    got = np.empty((n, n), dtype=np.float64)
+    for g in range(G):
+        piece = bufs[g].cpu().numpy()
+        assert np.all(piece[:, n:] == 7.0)                       # the padding of the leading dimension stays
+        for i, kb in enumerate(owned[g]):
+            got[:, kb * block:(kb + 1) * block] = piece[i * block:(i + 1) * block, :n].T
+    assert np.array_equal(got, want)
+    torch.cuda.set_device(0)
 
 
 @pytest.mark.gpu
