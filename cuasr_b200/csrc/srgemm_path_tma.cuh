@@ -4,31 +4,36 @@
 // Same role as srgemm_path_kernel (the device counterpart of the reference's legacy routine cpu_fwgemm_naive,
 // test/regress/include/fwgpu/cpu_srgemm.hpp:20-48), same staging as srgemm_tma_kernel: one persistent CTA per SM,
 // a producer lane that feeds a ring of shared-memory stages with TMA tile loads, eight consumer warps over a
-// 128 x 128 tile with an 8 x 8 micro-tile per lane.  What is new is the second accumulator set: idx[8][8] holds the
-// k of the best product so far.  Every output element lives in one lane, and that lane meets the K range in
-// ascending order (stage after stage, chunk after chunk), so "the first k that gives the best value" needs no
-// comparison between lanes; K is never split over CTAs here for the same reason.
+// 128 x 128 tile with an 8 x 8 micro-tile per lane.
 //
-// The contraction keeps the two-instruction form of the plain kernel (one packed or two scalar adds and one
-// three-input min/max per two products).  A product that IMPROVES an element is rare after the first few k (the
-// n-th product of a random sequence is a new minimum with probability 1/n), so the index is not updated with
-// selects in every step: each row of eight folds is followed by one test "did anything in this row change", and
-// only then the row is replayed element by element in k order to find out which k it was.
-// Ragged K: out-of-range operand elements are NaN (TMA fill), and a NaN product never compares as an improvement.
+// The contraction is the plain kernel's: per element and four k, two packed (or four scalar) adds and two
+// three-input min/max.  A product that IMPROVES an element is rare after the first few k (the n-th product of a
+// random sequence is a new minimum with probability 1/n), so nothing per product is spent on the index: each row
+// of eight elements is followed by one test "did any bit of this row change over these four k" (one three-input
+// logic instruction per element), and only then the row is replayed product by product, in k order, from the
+// operand registers, and the k of every improvement is stored straight to the parent matrix.  Every output element
+// lives in one lane, and that lane meets the K range in ascending order, so its stores to one parent element are
+// ordered and "the first k that gives the best value" needs no comparison between lanes; K is never split over
+// CTAs here for the same reason.  An element that never improves keeps the parent it came with: the parent matrix
+// is not read at all.
+// Ragged K and ragged tiles: out-of-range operand elements are NaN (TMA fill), and a NaN product never compares as
+// an improvement.
 #pragma once
 
 #include "srgemm_tma.cuh"
 
 namespace cuasr_b200 {
 
-__device__ __forceinline__ void lds8(uint32_t addr, float (&v)[2]) {
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "r"(addr));
+__device__ __forceinline__ float lds4(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
 }
 
 struct PathTmaParams {
   int M, N, K;
   float* dist;      long long d_row, d_col;     // dist(m, n) at dist[m * d_row + n * d_col], read and written
-  int32_t* parent;  long long p_row, p_col;     // same shape, read and written
+  int32_t* parent;  long long p_row, p_col;     // same shape; written where an element improves, never read
   int k_offset;                                 // added to every recorded k
   int tiles_m, tiles_n;
   unsigned int* status;
@@ -42,6 +47,9 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                        const PathTmaParams p) {
   constexpr int TK = kTileKBytes / 4;   // 32 k per stage
   constexpr int kChunks = TK / 4;       // 8 chunks of 16 bytes
+  // the replay of a row takes its operands from the registers of the chunk when both were loaded along k (the
+  // other layouts transpose while loading and would spill)
+  constexpr bool kReplayFromRegisters = kAK && kBK;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -103,7 +111,6 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   auto best3 = [](float x, float y, float z) { return kMaximize ? max3(x, y, z) : min3(x, y, z); };
 
   float acc[8][8];
-  int32_t idx[8][8];
 
   uint32_t it = 0;
   for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -117,9 +124,7 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int m = m_base + row_of(i), n = n_base + col_of(j);
-        const bool in = m < p.M && n < p.N;
-        acc[i][j] = in ? p.dist[m * p.d_row + n * p.d_col] : 0.0f;
-        idx[i][j] = in ? p.parent[m * p.p_row + n * p.p_col] : 0;
+        acc[i][j] = (m < p.M && n < p.N) ? p.dist[m * p.d_row + n * p.d_col] : 0.0f;
       }
 
     for (int kt = 0; kt < k_tiles; ++kt, ++it) {
@@ -128,19 +133,17 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const uint32_t sa = smem_base + s * kStageBytes;
       const uint32_t sb = sa + kOperandStageBytes;
 #pragma unroll 1
-      for (int step = 0; step < 2 * kChunks; ++step) {
-        // two k per step (the two accumulator sets leave room for no more operand registers):
-        // a[i][e] = A(row i, k = 2 * step + e)
-        const int chunk = step >> 1, half = step & 1;
-        float a[8][2], b[8][2];
+      for (int chunk = 0; chunk < kChunks; ++chunk) {
+        // a[i][e] = A(row i, k = 4 * chunk + e), b[j][e] = B(k = 4 * chunk + e, column j)
+        float a[8][4], b[8][4];
         if (kAK) {
-          const uint32_t base = sa + a_base + (((chunk ^ lr) & 7) << 4) + half * 8;
+          const uint32_t base = sa + a_base + (((chunk ^ lr) & 7) << 4);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) lds8(base + i * 1024, a[i]);
+          for (int i = 0; i < 8; ++i) lds16(base + i * 1024, a[i]);
         } else {
-          const uint32_t base = sa + a_base + step * (2 * kTileM * 4);
+          const uint32_t base = sa + a_base + chunk * (4 * kTileM * 4);
 #pragma unroll
-          for (int e = 0; e < 2; ++e)
+          for (int e = 0; e < 4; ++e)
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
               float v[4];
@@ -150,14 +153,14 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
         }
         if (kBK) {
-          const uint32_t base0 = sb + b_base + (((chunk ^ lc) & 7) << 4) + half * 8;
-          const uint32_t base1 = sb + b_base + (((chunk ^ (lc + 4)) & 7) << 4) + half * 8;
+          const uint32_t base0 = sb + b_base + (((chunk ^ lc) & 7) << 4);
+          const uint32_t base1 = sb + b_base + (((chunk ^ (lc + 4)) & 7) << 4);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) lds8(((j & 1) ? base1 : base0) + j * 512, b[j]);
+          for (int j = 0; j < 8; ++j) lds16(((j & 1) ? base1 : base0) + j * 512, b[j]);
         } else {
-          const uint32_t base = sb + b_base + step * (2 * kTileN * 4);
+          const uint32_t base = sb + b_base + chunk * (4 * kTileN * 4);
 #pragma unroll
-          for (int e = 0; e < 2; ++e)
+          for (int e = 0; e < 4; ++e)
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
               float v[4];
@@ -166,27 +169,29 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
               for (int t = 0; t < 4; ++t) b[g * 4 + t][e] = v[t];
             }
         }
-        const int32_t k0 = kt * TK + step * 2 + p.k_offset;
+        const int32_t k0 = kt * TK + chunk * 4 + p.k_offset;
         // The rows are software-pipelined by one: the folds of row i + 1 are issued before the test on row i, so
         // that the chain add -> fold -> "anything changed?" -> branch of one row runs under the arithmetic of the next.
-        float lo[2][8], hi[2][8], next[2][8];
+        float next[2][8];
         uint32_t any[2];
         auto fold_row = [&](int i, int buf) {
-          uint32_t diff[8];
+          uint32_t changed = 0;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
+            float s0, s1, s2, s3;
             if constexpr (kAK && kBK) {
-              unpack2(add2(pack2(a[i][0], a[i][1]), pack2(b[j][0], b[j][1])), lo[buf][j], hi[buf][j]);
+              unpack2(add2(pack2(a[i][0], a[i][1]), pack2(b[j][0], b[j][1])), s0, s1);
+              unpack2(add2(pack2(a[i][2], a[i][3]), pack2(b[j][2], b[j][3])), s2, s3);
             } else {
-              lo[buf][j] = a[i][0] + b[j][0];
-              hi[buf][j] = a[i][1] + b[j][1];
+              s0 = a[i][0] + b[j][0]; s1 = a[i][1] + b[j][1];
+              s2 = a[i][2] + b[j][2]; s3 = a[i][3] + b[j][3];
             }
-            next[buf][j] = best3(acc[i][j], lo[buf][j], hi[buf][j]);
+            next[buf][j] = best3(best3(acc[i][j], s0, s1), s2, s3);
             // the folds only ever move a value in one direction, so the bit patterns differ exactly where a
             // value improved
-            diff[j] = __float_as_uint(next[buf][j]) ^ __float_as_uint(acc[i][j]);
+            changed |= __float_as_uint(next[buf][j]) ^ __float_as_uint(acc[i][j]);
           }
-          any[buf] = ((diff[0] | diff[1]) | (diff[2] | diff[3])) | ((diff[4] | diff[5]) | (diff[6] | diff[7]));
+          any[buf] = changed;
         };
         fold_row(0, 0);
 #pragma unroll
@@ -194,12 +199,47 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const int buf = i & 1;
           if (i + 1 < 8) fold_row(i + 1, buf ^ 1);
           if (any[buf] != 0) {
-            // something in this row improved: replay its two k steps in order to see which one it was
+            // Something in this row improved: replay its four k in order to see which ones it was.  Where the
+            // registers do not reach, the operands are read again from the stage (it stays put until this warp
+            // releases it), so the replay holds on to none of the registers of the loop around it.  The opaque
+            // zero keeps the addresses from being computed ahead of the loop.
+            int zero;
+            asm volatile("mov.s32 %0, 0;" : "=r"(zero));
+            const int m = m_base + row_of(i) + zero;
+            float ar[4];
+            if constexpr (kReplayFromRegisters) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) ar[e] = a[i][e];
+            } else if (kAK) {
+              lds16(sa + a_base + (((chunk ^ lr) & 7) << 4) + i * 1024 + zero, ar);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                ar[e] = lds4(sa + a_base + (chunk * 4 + e) * (kTileM * 4) + ((i % 4) + 32 * (i / 4)) * 4 + zero);
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
+              float br[4];
+              if constexpr (kReplayFromRegisters) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) br[e] = b[j][e];
+              } else if (kBK) {
+                lds16(sb + b_base + (((chunk ^ (lc + 4 * (j & 1))) & 7) << 4) + j * 512 + zero, br);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  br[e] = lds4(sb + b_base + (chunk * 4 + e) * (kTileN * 4) + ((j % 4) + 16 * (j / 4)) * 4 + zero);
+              }
               float cur = acc[i][j];
-              if (better(lo[buf][j], cur)) { cur = lo[buf][j]; idx[i][j] = k0; }
-              if (better(hi[buf][j], cur)) { idx[i][j] = k0 + 1; }
+              int32_t k_best = 0;
+              bool improved = false;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float sum = ar[e] + br[e];
+                if (better(sum, cur)) { cur = sum; k_best = k0 + e; improved = true; }
+              }
+              const int n = n_base + col_of(j) + zero;
+              if (improved && m < p.M && n < p.N) p.parent[m * p.p_row + n * p.p_col] = k_best;
             }
           }
 #pragma unroll
@@ -210,15 +250,15 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
 
+    // (the opaque zero: the addresses are computed here again instead of being carried through the loop above)
+    int zero;
+    asm volatile("mov.s32 %0, 0;" : "=r"(zero));
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int m = m_base + row_of(i), n = n_base + col_of(j);
-        if (m < p.M && n < p.N) {
-          p.dist[m * p.d_row + n * p.d_col] = acc[i][j];
-          p.parent[m * p.p_row + n * p.p_col] = idx[i][j];
-        }
+        const int m = m_base + row_of(i) + zero, n = n_base + col_of(j) + zero;
+        if (m < p.M && n < p.N) p.dist[m * p.d_row + n * p.d_col] = acc[i][j];
       }
   }
 }
