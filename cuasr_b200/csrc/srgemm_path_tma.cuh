@@ -10,8 +10,9 @@
 // three-input min/max.  A product that IMPROVES an element is rare after the first few k (the n-th product of a
 // random sequence is a new minimum with probability 1/n), so nothing per product is spent on the index: each row
 // of eight elements is followed by one test "did any bit of this row change over these four k" (one three-input
-// logic instruction per element), and only then the row is replayed product by product, in k order, from the
-// operand registers, and the k of every improvement is stored straight to the parent matrix.  Every output element
+// logic instruction per element), and only then the improved elements of the row are noted in a bit mask.  After
+// the last row a loop runs once per noted element: it forms the four products again from the stage, takes the first
+// k that attains their best, and stores that k straight to the parent matrix.  Every output element
 // lives in one lane, and that lane meets the K range in ascending order, so its stores to one parent element are
 // ordered and "the first k that gives the best value" needs no comparison between lanes; K is never split over
 // CTAs here for the same reason.  An element that never improves keeps the parent it came with: the parent matrix
@@ -47,9 +48,6 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                        const PathTmaParams p) {
   constexpr int TK = kTileKBytes / 4;   // 32 k per stage
   constexpr int kChunks = TK / 4;       // 8 chunks of 16 bytes
-  // the replay of a row takes its operands from the registers of the chunk when both were loaded along k (the
-  // other layouts transpose while loading and would spill)
-  constexpr bool kReplayFromRegisters = kAK && kBK;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -170,10 +168,9 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
         }
         const int32_t k0 = kt * TK + chunk * 4 + p.k_offset;
-        // The rows are software-pipelined by one: the folds of row i + 1 are issued before the test on row i, so
-        // that the chain add -> fold -> "anything changed?" -> branch of one row runs under the arithmetic of the next.
-        float next[2][8];
-        uint32_t any[2];
+        float next[4][8];
+        uint32_t any[4];
+        uint32_t improved_lo = 0, improved_hi = 0;     // bit 8 i + j: element (i, j) improved in this chunk
         auto fold_row = [&](int i, int buf) {
           uint32_t changed = 0;
 #pragma unroll
@@ -193,57 +190,66 @@ srgemm_path_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           }
           any[buf] = changed;
         };
+        // Two rows per test, and the test on one pair of rows is issued after the folds of the next pair, so that
+        // the chain add -> fold -> "anything changed?" -> branch runs under the arithmetic of other rows.
         fold_row(0, 0);
+        fold_row(1, 1);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int buf = i & 1;
-          if (i + 1 < 8) fold_row(i + 1, buf ^ 1);
-          if (any[buf] != 0) {
-            // Something in this row improved: replay its four k in order to see which ones it was.  Where the
-            // registers do not reach, the operands are read again from the stage (it stays put until this warp
-            // releases it), so the replay holds on to none of the registers of the loop around it.  The opaque
-            // zero keeps the addresses from being computed ahead of the loop.
-            int zero;
-            asm volatile("mov.s32 %0, 0;" : "=r"(zero));
-            const int m = m_base + row_of(i) + zero;
-            float ar[4];
-            if constexpr (kReplayFromRegisters) {
+        for (int i = 0; i < 8; i += 2) {
+          const int buf = i & 2;
+          if (i + 2 < 8) {
+            fold_row(i + 2, buf ^ 2);
+            fold_row(i + 3, (buf ^ 2) + 1);
+          }
+          if (__builtin_expect((any[buf] | any[buf + 1]) != 0, 0)) {
+            // something in these rows improved: note which elements, the k are looked up after the last row
+            uint32_t bits = 0;
 #pragma unroll
-              for (int e = 0; e < 4; ++e) ar[e] = a[i][e];
-            } else if (kAK) {
-              lds16(sa + a_base + (((chunk ^ lr) & 7) << 4) + i * 1024 + zero, ar);
-            } else {
+            for (int r = 0; r < 2; ++r)
 #pragma unroll
-              for (int e = 0; e < 4; ++e)
-                ar[e] = lds4(sa + a_base + (chunk * 4 + e) * (kTileM * 4) + ((i % 4) + 32 * (i / 4)) * 4 + zero);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float br[4];
-              if constexpr (kReplayFromRegisters) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) br[e] = b[j][e];
-              } else if (kBK) {
-                lds16(sb + b_base + (((chunk ^ (lc + 4 * (j & 1))) & 7) << 4) + j * 512 + zero, br);
-              } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  br[e] = lds4(sb + b_base + (chunk * 4 + e) * (kTileN * 4) + ((j % 4) + 16 * (j / 4)) * 4 + zero);
-              }
-              float cur = acc[i][j];
-              int32_t k_best = 0;
-              bool improved = false;
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float sum = ar[e] + br[e];
-                if (better(sum, cur)) { cur = sum; k_best = k0 + e; improved = true; }
-              }
-              const int n = n_base + col_of(j) + zero;
-              if (improved && m < p.M && n < p.N) p.parent[m * p.p_row + n * p.p_col] = k_best;
-            }
+              for (int j = 0; j < 8; ++j)
+                if (better(next[buf + r][j], acc[i + r][j])) bits |= 1u << (8 * r + j);
+            if (i < 4) improved_lo |= bits << (8 * i);
+            else       improved_hi |= bits << (8 * (i - 4));
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[i][j] = next[buf][j];
+          for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[i + r][j] = next[buf + r][j];
+        }
+        // One pass per improved element of this lane; most chunks have none.  The improvements of an element are
+        // strict, so its new value is the best of the four products and the k of the last improvement is the
+        // first k that attains it.  The operands are read again from the stage (it stays put until this warp
+        // releases it): the loop is ordinary code with computed addresses, one copy of it per chunk.
+        while (__builtin_expect((improved_lo | improved_hi) != 0, 0)) {
+          int bit;
+          if (improved_lo != 0) { bit = __ffs(improved_lo) - 1; improved_lo &= improved_lo - 1; }
+          else                  { bit = 31 + __ffs(improved_hi); improved_hi &= improved_hi - 1; }
+          const int i = bit >> 3, j = bit & 7;
+          float ar[4], br[4];
+          if (kAK) {
+            lds16(sa + a_base + (((chunk ^ lr) & 7) << 4) + i * 1024, ar);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              ar[e] = lds4(sa + a_base + (chunk * 4 + e) * (kTileM * 4) + ((i % 4) + 32 * (i / 4)) * 4);
+          }
+          if (kBK) {
+            lds16(sb + b_base + (((chunk ^ (lc + 4 * (j & 1))) & 7) << 4) + j * 512, br);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              br[e] = lds4(sb + b_base + (chunk * 4 + e) * (kTileN * 4) + ((j % 4) + 16 * (j / 4)) * 4);
+          }
+          float best = ar[0] + br[0];
+          int e_first = 0;
+#pragma unroll
+          for (int e = 1; e < 4; ++e) {
+            const float sum = ar[e] + br[e];
+            if (better(sum, best)) { best = sum; e_first = e; }
+          }
+          const int m = m_base + row_of(i), n = n_base + col_of(j);
+          if (m < p.M && n < p.N) p.parent[m * p.p_row + n * p.p_col] = k0 + e_first;
         }
       }
       __syncwarp();

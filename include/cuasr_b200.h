@@ -115,8 +115,8 @@ CUASR_B200_API int cuasr_b200_srgemm_push(const cuasr_b200_desc_t *desc, const c
  * desc: add_op MINIMUM or MAXIMUM, mul_op PLUS, dtype F32 or F64.  args: A, B, D (= the distances, read and
  * written; C, alpha, beta, workspace are ignored), split_k_slices = 1.  parent has D's layout, leading dimension
  * ld_parent, 32-bit signed entries.  fp32 operands with 16-byte aligned storage lines run on the TMA pipeline (the
- * index update is entered only for rows of the register tile in which some element improved), everything else on
- * an any-layout kernel. */
+ * index is looked up, and parent written, only for elements that improved; parent is never read there), everything
+ * else on an any-layout kernel. */
 CUASR_B200_API int cuasr_b200_srgemm_path(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args, int32_t *parent,
                                           int64_t ld_parent, int32_t k_offset);
 
