@@ -417,14 +417,18 @@ def run_ours(args, wl):
     else:
         a_part = A.numel() // world
         ranges = [(rank * a_part, (rank + 1) * a_part)]
-    hA = torch.empty(sum(b - a for a, b in ranges), dtype=tdt).pin_memory()
+    # the pinned buffers of a rank come from the memory next to its GPU's host link
+    from cuasr_b200.host_pipeline import numa_local
+    with numa_local(dev.index if dev.index is not None else 0) as numa:
+        hA = torch.empty(sum(b - a for a, b in ranges), dtype=tdt).pin_memory()
+        hB = torch.empty(B.numel(), dtype=tdt).pin_memory()
+        hC = torch.empty(share, dtype=tdt).pin_memory(); hC.fill_(fill)
+        hD = torch.empty(share, dtype=tdt).pin_memory(); hD.zero_()
     pos = 0
     for a, b in ranges:
         hA[pos:pos + b - a].copy_(A[a:b])
         pos += b - a
-    hB = torch.empty(B.numel(), dtype=tdt).pin_memory(); hB.copy_(B)
-    hC = torch.empty(share, dtype=tdt).pin_memory(); hC.fill_(fill)
-    hD = torch.empty(share, dtype=tdt).pin_memory()
+    hB.copy_(B)
     e2e_steps = max(1, min(args.steps, 5))
 
     def e2e_step():
@@ -505,7 +509,8 @@ def run_ours(args, wl):
                            l2="operands exceed the 126 MB L2" if es * (m * k + k * n) > 126e6 else
                               "L2 flushed between steps by the other operands' traffic: NO (operands fit L2)"),
             "e2e": {"value": round(wl.ops / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GOP/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
+                    "pinned_memory_numa_node": numa.node},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "roofline": {"bound": "CUDA cores (issue / register-file ports); HBM is orders of magnitude below",

@@ -45,6 +45,55 @@ def share_ranges(shared_elems: int, k_pieces: int, rank: int, world: int):
     return [(p * piece + rank * sub, p * piece + (rank + 1) * sub) for p in range(k_pieces)]
 
 
+def device_numa_node(device_index: int):
+    """(NUMA node the GPU's host link hangs off, CPUs of that node this process may run on), or (None, set()) where
+    the system does not say (no sysfs entry, a single node, a virtual machine that hides the topology)."""
+    import os
+
+    import torch
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None, set()
+        cpus = set()
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        return node, cpus & os.sched_getaffinity(0)
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None, set()
+
+
+class numa_local:
+    """`with numa_local(device_index):` runs the calling thread on the CPUs next to the GPU's host link for the
+    length of the block.  Pinned host buffers allocated inside get their pages from that node's memory (Linux
+    places pages on the node of the thread that first touches them), so the GPU's copies do not cross the link
+    between the CPU sockets; with eight GPUs of one box copying at once that link is otherwise the narrow spot.
+    Only this process's own CPU affinity is touched, and it is put back on exit.  `.node` is the node, or None
+    where the system does not tell (then the block runs unchanged)."""
+
+    def __init__(self, device_index: int):
+        self.node, self._cpus = device_numa_node(device_index)
+        self._before = None
+
+    def __enter__(self):
+        import os
+        if self._cpus:
+            self._before = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, self._cpus)
+        return self
+
+    def __exit__(self, *exc):
+        import os
+        if self._before is not None:
+            os.sched_setaffinity(0, self._before)
+        return False
+
+
 def _address(ref) -> int:
     return ref.data_ptr() if hasattr(ref, "data_ptr") else int(ref)
 
@@ -227,13 +276,15 @@ class HostSrgemm:
                 raise RuntimeError(f"SRGEMM failed on {what}: {st!r}")
             self.launches += 1
 
-    def _first_chunk_by_k_pieces(self, args, shared_dev, shared_host, extras) -> None:
-        """Chunk 0 as k_pieces accumulating launches, piece p as soon as K piece p of the shared operand is there."""
+    def _first_chunk_by_k_pieces(self, args, shared_dev, shared_host, extras, first_piece, inputs) -> None:
+        """Chunk 0 as k_pieces accumulating launches, piece p as soon as K piece p of the shared operand is there.
+        first_piece: arrival of K piece 0 (already on its way); inputs: arrival of the chunk's other operand and C."""
         torch = self.torch
         kp = self.k // self.k_pieces
         (m, n, _), es = args.problem_size, self.es
+        self.s_run.wait_event(inputs)
         for p in range(self.k_pieces):
-            self.s_run.wait_event(self._bring_shared_piece(shared_dev, shared_host, p))
+            self.s_run.wait_event(first_piece if p == 0 else self._bring_shared_piece(shared_dev, shared_host, p))
             if self.col_c:      # A column-major: K piece = columns of A; B chunk column-major: K piece = rows of B
                 a = (_address(args.ref_A[0]) + p * kp * self.lda * es, self.lda)
                 b = (_address(args.ref_B[0]) + p * kp * es, self.ldb)
@@ -277,13 +328,19 @@ class HostSrgemm:
             self._open_exchange(start)
         for j in range(self.chunks):
             args, moving, out = self._chunk_args(j)
+            by_pieces = j == 0 and self.k_pieces > 1
+            # K piece 0 of the shared operand goes first: with several ranks its exchange then runs under the copies
+            # of the chunk's own inputs
+            first_piece = self._bring_shared_piece(shared_dev, shared_host, 0) if by_pieces else None
             with torch.cuda.stream(self.s_in):
                 moving_dev[moving].copy_(moving_host[moving], non_blocking=True)
                 self.dC[out].copy_(hC[out], non_blocking=True)
             extras = self.extra(j, out.start * self.es) if self.extra else []
             done = torch.cuda.Event()
-            if j == 0 and self.k_pieces > 1:
-                self._first_chunk_by_k_pieces(args, shared_dev, shared_host, extras)
+            if by_pieces:
+                inputs = torch.cuda.Event()
+                inputs.record(self.s_in)
+                self._first_chunk_by_k_pieces(args, shared_dev, shared_host, extras, first_piece, inputs)
             else:
                 arrived = torch.cuda.Event()
                 arrived.record(self.s_in)

@@ -105,3 +105,17 @@ def test_shares_of_the_shared_operand_tile_it_exactly_once():
         assert (covered == 1).all()
     with pytest.raises(ValueError):
         share_ranges(100, 4, 0, 3)
+
+
+def test_numa_local_leaves_the_process_as_it_found_it():
+    """numa_local moves the process next to a GPU's host link for the length of a block and puts the CPU affinity
+    back; where the system does not tell the topology (no GPU here) it does nothing at all."""
+    import os
+    from cuasr_b200.host_pipeline import device_numa_node, numa_local
+    before = os.sched_getaffinity(0)
+    node, cpus = device_numa_node(0)
+    assert node is None or cpus <= before
+    with numa_local(0) as where:
+        inside = os.sched_getaffinity(0)
+        assert inside <= before and (where.node is not None or inside == before)
+    assert os.sched_getaffinity(0) == before
