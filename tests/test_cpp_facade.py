@@ -93,3 +93,15 @@ def test_rehosted_reference_examples(cuda_device):
     res = subprocess.run([BINARY], capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "ALL OK" in res.stdout
+
+
+@pytest.mark.gpu
+def test_multi_gpu_solve_from_a_plain_cpp_host(cuda_device):
+    """cuasr_b200_apsp_multi called from a C++ program with cudaMalloc'ed buffers (no Python, no NCCL): repeated
+    squaring and blocked Floyd-Warshall on 1, 2 and 4 GPUs as far as the box has them, against a host
+    Floyd-Warshall."""
+    binary = os.path.join(ROOT, "tests", "cpp", "apsp_multi_host")
+    assert os.path.exists(binary), "build it with __graft_entry__.build()"
+    res = subprocess.run([binary], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "ALL OK" in res.stdout
