@@ -43,6 +43,7 @@ class ApspArgs(ctypes.Structure):          # cuasr_b200_apsp_args_t
         ("D", ctypes.c_void_p), ("ldd", ctypes.c_int64),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("stream", ctypes.c_void_p),
+        ("parent", ctypes.c_void_p), ("ld_parent", ctypes.c_int64),
     ]
 
 

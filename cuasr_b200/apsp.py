@@ -374,7 +374,8 @@ REPEATED_SQUARING, BLOCKED_FLOYD_WARSHALL = 0, 1
 
 
 def _apsp_args(dtype: DType, algorithm: int, n: int, D=0, ldd: Optional[int] = None, block: int = 0,
-               iterations: int = 0, workspace=0, workspace_bytes: int = 0, stream: int = 0):
+               iterations: int = 0, workspace=0, workspace_bytes: int = 0, stream: int = 0, parent=0,
+               ld_parent: Optional[int] = None):
     from . import _lib
 
     a = _lib.ApspArgs()
@@ -382,6 +383,7 @@ def _apsp_args(dtype: DType, algorithm: int, n: int, D=0, ldd: Optional[int] = N
     a.D, a.ldd = int(D) or None, int(n if ldd is None else ldd)
     a.workspace, a.workspace_bytes = int(workspace) or None, int(workspace_bytes)
     a.stream = int(stream) or None
+    a.parent, a.ld_parent = int(parent) or None, int(n if ld_parent is None else ld_parent)
     return a
 
 
@@ -395,10 +397,13 @@ def device_solve_workspace_size(dtype: DType, algorithm: int, n: int, block: int
 
 
 def device_solve(D, n: int, dtype: DType = DType.F32, algorithm: int = BLOCKED_FLOYD_WARSHALL, ldd: Optional[int] = None,
-                 block: int = 0, iterations: int = 0, workspace=None, stream=None) -> Status:
+                 block: int = 0, iterations: int = 0, workspace=None, stream=None, parent=None,
+                 ld_parent: Optional[int] = None) -> Status:
     """cuasr_b200_apsp: closes the n x n distance matrix `D` (a torch CUDA tensor or a device address) in place on
     one GPU; enqueues on `stream` (default: the current torch stream) and returns.  `workspace`: a uint8 CUDA
-    tensor of at least `device_solve_workspace_size` bytes; allocated here when omitted."""
+    tensor of at least `device_solve_workspace_size` bytes; allocated here when omitted.  `parent`: optional int32
+    n x n matrix (column-major like D, filled with -1 by the caller) that receives, for every pair whose distance
+    improved, a vertex k with D[i, j] == D[i, k] + D[k, j] (`walk` turns it into vertex sequences)."""
     import ctypes
 
     import torch
@@ -410,8 +415,32 @@ def device_solve(D, n: int, dtype: DType = DType.F32, algorithm: int = BLOCKED_F
                                 device="cuda")
     s = torch.cuda.current_stream().cuda_stream if stream is None else getattr(stream, "cuda_stream", stream)
     ptr = D.data_ptr() if hasattr(D, "data_ptr") else int(D)
-    a = _apsp_args(dtype, algorithm, n, ptr, ldd, block, iterations, workspace.data_ptr(), workspace.numel(), s)
+    par = 0 if parent is None else (parent.data_ptr() if hasattr(parent, "data_ptr") else int(parent))
+    a = _apsp_args(dtype, algorithm, n, ptr, ldd, block, iterations, workspace.data_ptr(), workspace.numel(), s, par,
+                   ld_parent)
     return Status(_lib.load().cuasr_b200_apsp(ctypes.byref(a)))
+
+
+def walk(parent, i: int, j: int):
+    """The vertices of the shortest path i -> j, end points included, from the predecessor matrix a solve with
+    `parent` left behind: parent[i][j] = k >= 0 splits the path at k, a negative entry means the pair is joined by
+    an edge of the input (the caller checks beforehand that j can be reached at all).  `parent` is indexed
+    [i][j] (pass the transpose of the column-major device matrix)."""
+    path, todo = [i], [(i, j)]
+    steps = 0
+    while todo:
+        # a simple path over n vertices has at most n - 1 edges and n - 2 splits
+        steps += 1
+        if steps > 2 * len(parent):
+            raise ValueError("the predecessor matrix does not describe a simple path (zero-weight cycle?)")
+        u, v = todo.pop()
+        k = int(parent[u][v])
+        if k < 0:
+            path.append(v)
+        else:
+            todo.append((k, v))
+            todo.append((u, k))
+    return path
 
 
 def shard_squaring(dtype: DType, n: int, col0: int, cols: int, d_cur: int, ld_cur: int, d_next: int, ld_next: int,

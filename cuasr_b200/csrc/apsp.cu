@@ -117,7 +117,81 @@ FwLayout fw_layout(const cuasr_b200_apsp_args_t& a) {
   return l;
 }
 
+// The path-tracking product of the solves with predecessors: dist <- min(dist, A (x) B) in place, the k of every
+// improvement (plus k_offset) to `parent`.
+int path_product(const cuasr_b200_apsp_args_t& a, int m, int nn, int k, const void* A, long long lda, const void* B,
+                 long long ldb, void* dist, long long ldd, int32_t* parent, int k_offset) {
+  const cuasr_b200_desc_t desc = minplus_desc(a.dtype);
+  cuasr_b200_args_t s = minplus_args(a.dtype, m, nn, k, A, lda, B, ldb, dist, ldd, dist, ldd, nullptr, 0, a.stream);
+  return cuasr_b200_srgemm_path(&desc, &s, parent, a.ld_parent, k_offset);
+}
+
+cudaError_t copy_block(const cuasr_b200_apsp_args_t& a, void* dst, size_t ld_dst, const void* src, size_t ld_src,
+                       size_t rows, size_t cols) {
+  const size_t es = elem_size(a.dtype);
+  return cudaMemcpy2DAsync(dst, ld_dst * es, src, ld_src * es, rows * es, cols, cudaMemcpyDeviceToDevice,
+                           static_cast<cudaStream_t>(a.stream));
+}
+
+// Repeated squaring with predecessors: D <- min(D, D' (x) D') in place, D' a copy of D taken before each squaring.
+int squaring_with_parents(const cuasr_b200_apsp_args_t& a) {
+  void* copy = a.workspace;               // n x n, leading dimension n
+  const int iterations = a.iterations > 0 ? a.iterations : std::max(1, ceil_log2(a.n));
+  for (int it = 0; it < iterations; ++it) {
+    if (copy_block(a, copy, a.n, a.D, a.ldd, a.n, a.n) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+    const int st = path_product(a, a.n, a.n, a.n, copy, a.n, copy, a.n, a.D, a.ldd, a.parent, 0);
+    if (st != CUASR_STATUS_SUCCESS) return st;
+  }
+  return CUASR_STATUS_SUCCESS;
+}
+
+// Blocked Floyd-Warshall with predecessors.  Same phases as below, every product the path-tracking one, and every
+// finished piece is copied back into D before the next phase reads D: the path-tracking product records a k only
+// for a STRICT improvement, so a phase that meets values an earlier phase has already produced (the diagonal block
+// inside the panels, the panels inside the full update) records nothing for them, in particular not the trivial
+// "improvement" through an end point of the pair itself (D[i, i] == 0).
+int floyd_warshall_with_parents(const cuasr_b200_apsp_args_t& a) {
+  const size_t es = elem_size(a.dtype);
+  const int n = a.n, b = block_of(a);
+  const FwLayout l = fw_layout(a);
+  char* ws = static_cast<char*>(a.workspace);
+  char* D = static_cast<char*>(a.D);
+  void* p_col = ws + l.p_col;             // n x bk, leading dimension n
+  void* p_row = ws + l.p_row;             // bk x n, leading dimension b
+  void* diag[2] = {ws + l.diag[0], ws + l.diag[1]};   // bk x bk, leading dimension b
+  for (int k0 = 0; k0 < n; k0 += b) {
+    const int bk = std::min(b, n - k0);
+    char* dkk = D + (static_cast<size_t>(k0) + static_cast<size_t>(k0) * a.ldd) * es;
+    char* col = D + static_cast<size_t>(k0) * a.ldd * es;
+    char* row = D + static_cast<size_t>(k0) * es;
+    int32_t* parent_kk = a.parent + k0 + static_cast<size_t>(k0) * a.ld_parent;
+    int32_t* parent_col = a.parent + static_cast<size_t>(k0) * a.ld_parent;
+    int32_t* parent_row = a.parent + k0;
+    // phase 1: paths inside the block, by squaring the diagonal block in place against a copy of itself
+    for (int it = 0; it < std::max(1, ceil_log2(bk)); ++it) {
+      if (copy_block(a, diag[0], b, dkk, a.ldd, bk, bk) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+      const int st = path_product(a, bk, bk, bk, diag[0], b, diag[0], b, dkk, a.ldd, parent_kk, k0);
+      if (st != CUASR_STATUS_SUCCESS) return st;
+    }
+    if (copy_block(a, diag[0], b, dkk, a.ldd, bk, bk) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;   // the closed block
+    // phase 2: both panels through the closed block, in place against copies of themselves
+    if (copy_block(a, p_col, n, col, a.ldd, n, bk) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+    int st = path_product(a, n, bk, bk, p_col, n, diag[0], b, col, a.ldd, parent_col, k0);
+    if (st != CUASR_STATUS_SUCCESS) return st;
+    if (copy_block(a, p_row, b, row, a.ldd, bk, n) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+    st = path_product(a, bk, n, bk, diag[0], b, p_row, b, row, a.ldd, parent_row, k0);
+    if (st != CUASR_STATUS_SUCCESS) return st;
+    // phase 3: everything through the two finished panels, in place (the operands are copies)
+    if (copy_block(a, p_col, n, col, a.ldd, n, bk) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+    if (copy_block(a, p_row, b, row, a.ldd, bk, n) != cudaSuccess) return CUASR_STATUS_ERROR_INTERNAL;
+    st = path_product(a, n, n, bk, p_col, n, p_row, b, D, a.ldd, a.parent, k0);
+    if (st != CUASR_STATUS_SUCCESS) return st;
+  }
+  return CUASR_STATUS_SUCCESS;
+}
+
 int squaring(const cuasr_b200_apsp_args_t& a) {
+  if (a.parent != nullptr) return squaring_with_parents(a);
   const cuasr_b200_desc_t desc = minplus_desc(a.dtype);
   const size_t es = elem_size(a.dtype), n = a.n;
   const size_t matrix = align_up(n * n * es, 256);
@@ -147,6 +221,7 @@ int squaring(const cuasr_b200_apsp_args_t& a) {
 }
 
 int floyd_warshall(const cuasr_b200_apsp_args_t& a) {
+  if (a.parent != nullptr) return floyd_warshall_with_parents(a);
   const cuasr_b200_desc_t desc = minplus_desc(a.dtype);
   const size_t es = elem_size(a.dtype);
   const int n = a.n, b = block_of(a);
@@ -211,6 +286,10 @@ int cuasr_b200_apsp(const cuasr_b200_apsp_args_t* args) {
                               : fw_layout(*args).srgemm;
   if (args->workspace == nullptr || args->workspace_bytes < required) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
   if (reinterpret_cast<uintptr_t>(args->workspace) % 256 != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+  if (args->parent != nullptr) {
+    if (args->ld_parent < args->n) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+    if (reinterpret_cast<uintptr_t>(args->parent) % 4 != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+  }
   return args->algorithm == CUASR_APSP_REPEATED_SQUARING ? squaring(*args) : floyd_warshall(*args);
 }
 

@@ -42,6 +42,8 @@ typedef struct cuasr_b200_apsp_args {
   void *workspace;     /* at least cuasr_b200_apsp_workspace_size bytes, 256-byte aligned */
   size_t workspace_bytes;
   void *stream;        /* cudaStream_t */
+  int32_t *parent;     /* optional (NULL = distances only): n x n, column-major like D, see below */
+  int64_t ld_parent;   /* >= n, in elements */
 } cuasr_b200_apsp_args_t;
 
 /* Bytes of device scratch cuasr_b200_apsp needs: a second n x n matrix for repeated squaring; two panels and two
@@ -50,7 +52,16 @@ typedef struct cuasr_b200_apsp_args {
 CUASR_B200_API size_t cuasr_b200_apsp_workspace_size(const cuasr_b200_apsp_args_t *args);
 
 /* Enqueues the whole solve on args->stream and returns.  CUASR_STATUS_ERROR_WORKSPACE_NULL when the workspace is
- * missing or too small, CUASR_STATUS_ERROR_INVALID_PROBLEM for bad sizes or pointers. */
+ * missing or too small, CUASR_STATUS_ERROR_INVALID_PROBLEM for bad sizes or pointers.
+ *
+ * With `parent` set the solve also says how to walk the shortest paths: every product of the solve is the
+ * path-tracking one (cuasr_b200_srgemm_path), and whenever D[i, j] improves to D[i, k] + D[k, j] the vertex k goes
+ * to parent[i + j * ld_parent].  Entries that never improve keep what the caller put there (fill the matrix with a
+ * value that is no vertex, say -1, before the call).  Afterwards, for every pair with parent k >= 0:
+ * D[i, j] == D[i, k] + D[k, j] with k different from i and j, so the path i -> j is the path i -> k followed by the
+ * path k -> j, down to pairs without a parent, which are edges of the input.  This needs what shortest paths need
+ * anyway: D[i, i] == 0 and positive weights elsewhere (a zero-weight cycle would make the walk circular).
+ * The distances are the same bits as without `parent`; the same workspace size serves both. */
 CUASR_B200_API int cuasr_b200_apsp(const cuasr_b200_apsp_args_t *args);
 
 /* One squaring of a solve whose columns are sharded over GPUs: this rank owns columns [col0, col0 + cols) and

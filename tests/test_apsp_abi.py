@@ -214,3 +214,63 @@ def test_flags_raise_wait_and_a_wait_that_runs_out(cuda_device):
     assert device_status() == 0                                              # reading the status clears it
     assert lib.cuasr_b200_flag_wait(words.data_ptr(), 1, 1, 0, s) == int(Status.kErrorInvalidProblem)
     assert lib.cuasr_b200_flag_raise(ptrs, 9, 1, s) == int(Status.kErrorInvalidProblem)
+
+
+def test_walk_follows_a_predecessor_matrix():
+    P = [[-1] * 5 for _ in range(5)]
+    P[0][4], P[0][2], P[2][4] = 2, 1, 3                 # 0 -> 4 splits at 2; 0 -> 2 at 1; 2 -> 4 at 3
+    assert apsp.walk(P, 0, 4) == [0, 1, 2, 3, 4]
+    assert apsp.walk(P, 3, 4) == [3, 4]
+    with pytest.raises(ValueError):                     # a matrix that describes no path must not loop for ever
+        apsp.walk([[0, 1], [0, 1]], 0, 1)
+
+
+def test_predecessor_arguments_are_checked_without_a_device():
+    import ctypes
+    from cuasr_b200 import _lib
+    lib = _lib.load()
+    call = lambda **kw: Status(lib.cuasr_b200_apsp(ctypes.byref(apsp._apsp_args(**kw))))
+    ok = dict(dtype=DType.F32, algorithm=apsp.BLOCKED_FLOYD_WARSHALL, n=64, D=4096, workspace=8192, workspace_bytes=1 << 20,
+              parent=1 << 16)
+    assert call(**dict(ok, ld_parent=63)) == Status.kErrorInvalidProblem
+    assert call(**dict(ok, parent=(1 << 16) + 2)) == Status.kErrorMisalignedOperand
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("algorithm", [apsp.REPEATED_SQUARING, apsp.BLOCKED_FLOYD_WARSHALL])
+@pytest.mark.parametrize("n,ld,ldp,block,dt", [(512, 512, 512, 128, DType.F32), (1000, 1008, 1004, 256, DType.F32),
+                                               (300, 300, 300, 64, DType.F64)])
+def test_device_solve_with_predecessors(cuda_device, algorithm, n, ld, ldp, block, dt):
+    """The solve with `parent`: the same distances, bit for bit, and a predecessor matrix every entry of which
+    splits its pair into two shorter shortest paths; walking it gives paths made of edges of the input whose weights
+    add up to the distance."""
+    import torch
+    np_t = np.float32 if dt == DType.F32 else np.float64
+    w = _graph(n, 3 * n + block, np_t)
+    want = _closure(w)
+    buf = np.full((n, ld), 7.0, dtype=np_t)
+    buf[:, :n] = w.T
+    D = torch.from_numpy(buf).cuda()
+    P = torch.full((n, ldp), -1, dtype=torch.int32, device="cuda")
+    assert apsp.device_solve(D, n, dt, algorithm, ldd=ld, block=block, parent=P, ld_parent=ldp) == Status.kSuccess
+    torch.cuda.synchronize()
+    dist = D.cpu().numpy()[:, :n].T.astype(np.float64)          # dist[i, j]
+    par = P.cpu().numpy()[:, :n].T                              # par[i, j]
+    assert np.array_equal(dist, want)
+    assert np.all(P.cpu().numpy()[:, n:] == -1)                 # the padding of the predecessor matrix is untouched
+    i, j = np.nonzero(par >= 0)
+    k = par[i, j]
+    assert np.all((k != i) & (k != j) & (k < n))
+    assert np.array_equal(dist[i, j], dist[i, k] + dist[k, j])  # every predecessor splits its pair exactly
+    direct = par < 0
+    assert np.array_equal(dist[direct], w.astype(np.float64)[direct])   # no predecessor: an edge (or nothing) of the input
+    rng = np.random.default_rng(n)
+    checked = 0
+    for a, b in rng.integers(0, n, size=(400, 2)):
+        if a == b or not np.isfinite(dist[a, b]):
+            continue
+        path = apsp.walk(par, int(a), int(b))
+        assert path[0] == a and path[-1] == b and len(set(path)) == len(path)
+        assert sum(float(w[u, v]) for u, v in zip(path, path[1:])) == dist[a, b]
+        checked += 1
+    assert checked > 50
