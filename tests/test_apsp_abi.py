@@ -274,3 +274,30 @@ def test_device_solve_with_predecessors(cuda_device, algorithm, n, ld, ldp, bloc
         assert sum(float(w[u, v]) for u, v in zip(path, path[1:])) == dist[a, b]
         checked += 1
     assert checked > 50
+
+
+def test_multi_gpu_solve_stops_together_when_no_device_can_be_used():
+    """A GPU that cannot be selected fails its host thread before the first step; the threads agree on that at their
+    first barrier and all of them leave without launching anything (no thread is left waiting for the others).
+    Without any GPU every thread fails that way."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("the buffers below are not real")
+    st, _, _ = apsp.multi_device_solve(DType.F32, 256, [0, 1], [4096, 4096], [8192, 8192])
+    assert st == Status.kErrorInternal
+    st, _, _ = apsp.multi_device_solve(DType.F32, 256, [0, 1], [4096, 4096], workspaces=[4096, 8192], workspace_bytes=1 << 30,
+                                       algorithm=apsp.BLOCKED_FLOYD_WARSHALL, block=64)
+    assert st == Status.kErrorInternal
+
+
+@pytest.mark.gpu
+def test_multi_gpu_solve_stops_together_when_one_device_cannot_be_used(cuda_device):
+    """The same with one good GPU and an ordinal that does not exist: the good GPU's thread learns of the failure at
+    the first barrier and launches nothing."""
+    import torch
+    n = 256
+    D = [torch.zeros(n * n, dtype=torch.float32, device="cuda:0") for _ in range(2)]
+    st, _, _ = apsp.multi_device_solve(DType.F32, n, [0, 99], [D[0].data_ptr(), 4096], [D[1].data_ptr(), 8192])
+    assert st in (Status.kErrorInternal, Status.kErrorNotSupported)
+    torch.cuda.synchronize()
+    assert float(D[0].abs().sum()) == 0.0 and float(D[1].abs().sum()) == 0.0
