@@ -342,8 +342,23 @@ bool multi_valid(const cuasr_b200_apsp_multi_args_t* a) {
 // Per-GPU scratch of the sharded Floyd-Warshall solve, as offsets into the workspace.
 constexpr int kPanelBuffers = 3;
 struct MultiFwLayout {
-  size_t p_col[kPanelBuffers], p_row, diag[2], total;
+  size_t p_col[kPanelBuffers], p_row, diag[2], srgemm, total;
 };
+// What the SRGEMM launches of one GPU's share can use, at most, as their optional workspace (they run one after
+// the other on one stream, so one region serves all of them).  0 without a current device.
+size_t multi_srgemm_scratch(const cuasr_b200_apsp_multi_args_t& a) {
+  const cuasr_b200_desc_t desc = minplus_desc(a.dtype);
+  const void* any = reinterpret_cast<const void*>(static_cast<uintptr_t>(256));   // never dereferenced by the query
+  auto need = [&](int m, int nn, int k, long long lda, long long ldb, long long ldc) {
+    cuasr_b200_args_t s = minplus_args(a.dtype, m, nn, k, any, lda, any, ldb, any, ldc, const_cast<void*>(any), ldc,
+                                       nullptr, 0, nullptr);
+    return cuasr_b200_srgemm_optional_workspace_size(&desc, &s);
+  };
+  const int n = a.n, b = multi_block(a), cols = n / a.n_devices;
+  const long long ld = a.ldd;
+  return std::max(std::max(need(b, b, b, b, b, b), need(n, b, b, ld, b, ld)),
+                  std::max(need(b, cols, b, n, ld, ld), need(n, cols, b, n, b, ld)));
+}
 MultiFwLayout multi_fw_layout(const cuasr_b200_apsp_multi_args_t& a) {
   const size_t es = elem_size(a.dtype), n = a.n, b = multi_block(a), cols = n / a.n_devices;
   MultiFwLayout l;
@@ -351,7 +366,8 @@ MultiFwLayout multi_fw_layout(const cuasr_b200_apsp_multi_args_t& a) {
   for (int i = 0; i < kPanelBuffers; ++i) { l.p_col[i] = off; off = align_up(off + n * b * es, 256); }
   l.p_row = off; off = align_up(off + b * cols * es, 256);
   for (int i = 0; i < 2; ++i) { l.diag[i] = off; off = align_up(off + b * b * es, 256); }
-  l.total = off;
+  l.srgemm = off;
+  l.total = off + multi_srgemm_scratch(a);
   return l;
 }
 }  // namespace
@@ -373,7 +389,8 @@ int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
       if (a->devices[g] == a->devices[h]) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
   }
   if (fw) {
-    if (a->workspace == nullptr || a->workspace_bytes < multi_fw_layout(*a).total) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
+    // the part of the workspace the solve cannot do without; the SRGEMM scratch behind it is used when it is there
+    if (a->workspace == nullptr || a->workspace_bytes < multi_fw_layout(*a).srgemm) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
     for (int g = 0; g < G; ++g) {
       if (a->workspace[g] == nullptr) return CUASR_STATUS_ERROR_WORKSPACE_NULL;
       if (reinterpret_cast<uintptr_t>(a->workspace[g]) % 256 != 0) return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
@@ -453,6 +470,8 @@ int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
     char* D = static_cast<char*>(a->buf0[g]);
     void* p_row = ws + l.p_row;                               // b x cols, leading dimension b
     void* diag[2] = {ws + l.diag[0], ws + l.diag[1]};         // b x b
+    void* scratch = a->workspace_bytes > l.srgemm ? ws + l.srgemm : nullptr;
+    const size_t scratch_bytes = a->workspace_bytes - l.srgemm;
     cudaEvent_t done[kPanelBuffers] = {}, pushed = nullptr;
     bool events = cudaEventCreateWithFlags(&pushed, cudaEventDisableTiming) == cudaSuccess;
     for (int i = 0; i < kPanelBuffers; ++i)
@@ -460,7 +479,7 @@ int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
     if (!events) fail(CUASR_STATUS_ERROR_INTERNAL);
     auto product = [&](int m, int nn, int k, const void* A, long long lda, const void* B, long long ldb, const void* C,
                        long long ldc, void* out, long long ldo, int n_extra, void* const* extra) {
-      cuasr_b200_args_t s = minplus_args(a->dtype, m, nn, k, A, lda, B, ldb, C, ldc, out, ldo, nullptr, 0, stream);
+      cuasr_b200_args_t s = minplus_args(a->dtype, m, nn, k, A, lda, B, ldb, C, ldc, out, ldo, scratch, scratch_bytes, stream);
       return n_extra > 0 ? cuasr_b200_srgemm_push(&desc, &s, n_extra, extra) : cuasr_b200_srgemm(&desc, &s);
     };
     // phases 1 and 2 (column part) of block kb, by its owner: the closed diagonal block from a private copy, then

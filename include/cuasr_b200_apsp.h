@@ -131,7 +131,9 @@ typedef struct cuasr_b200_apsp_multi_args {
 CUASR_B200_API int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t *args);
 
 /* Bytes of per-GPU scratch cuasr_b200_apsp_multi needs (0 for repeated squaring, whose workspace is optional, and
- * for invalid arguments): three column panels, one row-panel piece and two diagonal blocks for Floyd-Warshall. */
+ * for invalid arguments): three column panels, one row-panel piece and two diagonal blocks for Floyd-Warshall, plus,
+ * when a device is current, what the SRGEMM launches can use to balance their last wave (that part is optional: a
+ * smaller workspace that still holds the panels and blocks is accepted). */
 CUASR_B200_API size_t cuasr_b200_apsp_multi_workspace_size(const cuasr_b200_apsp_multi_args_t *args);
 
 /* How the columns are dealt out by the repeated-squaring form of cuasr_b200_apsp_multi: first column and number of
