@@ -6,5 +6,5 @@ reference's `Srgemm` / `SrgemmSplitKParallel` host operators used by the tests a
 """
 from .semiring import DType, Layout, Op, RINGS, Status, annihilator, identity  # noqa: F401
 from .srgemm import (Arguments, Srgemm, SrgemmSplitKParallel, STATIC_SCRATCH_BYTES, device_status,  # noqa: F401
-                     launch_count, srgemm_path, srgemm_splitk_static)
+                     launch_count, pack_k_contiguous, srgemm_path, srgemm_splitk_static)
 from .host_pipeline import HostSrgemm  # noqa: F401,E402

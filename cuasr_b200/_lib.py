@@ -97,6 +97,9 @@ PROTOTYPES = {
                                              ctypes.c_void_p]),
     "cuasr_b200_flag_wait": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32,
                                             ctypes.c_void_p]),
+    "cuasr_b200_pack_k_contiguous": (ctypes.c_int, [ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                                    ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64,
+                                                    ctypes.c_void_p]),
     "cuasr_b200_device_status": (ctypes.c_int, [ctypes.c_void_p]),
     "cuasr_b200_last_kernel": (ctypes.c_char_p, []),
     "cuasr_b200_launch_count": (ctypes.c_uint64, []),

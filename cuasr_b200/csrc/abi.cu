@@ -777,6 +777,23 @@ int cuasr_b200_srgemm_path(const cuasr_b200_desc_t* desc, const cuasr_b200_args_
   return CUASR_STATUS_SUCCESS;
 }
 
+int cuasr_b200_pack_k_contiguous(int32_t dtype, const void* src, int64_t ld_src, int32_t src_k_contiguous, int32_t rows,
+                                 int32_t k, void* dst, int64_t ld_dst, void* stream) {
+  if (dtype != CUASR_F32 && dtype != CUASR_F64 && dtype != CUASR_S32 && dtype != CUASR_U32)
+    return CUASR_STATUS_ERROR_INVALID_DATA_TYPE;
+  if (src == nullptr || dst == nullptr || rows <= 0 || k <= 0 || ld_dst < k) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  if (ld_src < (src_k_contiguous ? k : rows)) return CUASR_STATUS_ERROR_INVALID_PROBLEM;
+  const size_t es = dtype == CUASR_F64 ? 8 : 4;
+  if (reinterpret_cast<uintptr_t>(src) % es != 0 || reinterpret_cast<uintptr_t>(dst) % es != 0)
+    return CUASR_STATUS_ERROR_MISALIGNED_OPERAND;
+  if (launch_repack(src, ld_src, src_k_contiguous != 0, rows, k, k, 0ull, dst, ld_dst, es,
+                    static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return CUASR_STATUS_ERROR_INTERNAL;
+  g_launches.fetch_add(1);
+  t_last_kernel = "pack";
+  return CUASR_STATUS_SUCCESS;
+}
+
 int cuasr_b200_device_status(void* stream) {
   DeviceState* dev = nullptr;
   if (!device_state(&dev)) return -1;

@@ -31,7 +31,7 @@ from __future__ import annotations
 from typing import Optional
 
 from .semiring import DType, Layout, Op, Status
-from .srgemm import Arguments, Srgemm
+from .srgemm import Arguments, Srgemm, pack_k_contiguous
 
 
 def share_ranges(shared_elems: int, k_pieces: int, rank: int, world: int):
@@ -153,6 +153,16 @@ class HostSrgemm:
         self.shared_on_device = bool(shared_on_device)
         if self.shared_on_device:
             self.k_pieces = 1
+        # Every chunk multiplies by the same shared operand.  Where its storage lines run along M (or N) the kernel
+        # would make a K-contiguous copy of it for every launch; the pipeline makes that copy once, K piece by K
+        # piece as the operand arrives, and hands the launches the copy (a row-major A, a column-major B).
+        self.packed = None
+        if self.chunkable and shared_lines_are_k and not self.shared_on_device:
+            rows = m if col_c else n
+            self.packed = torch.empty(rows * k, dtype=tdt, device=device)
+            self.op_packed = Srgemm(operator.add_op, operator.mul_op, operator.dtype,
+                                    Layout.ROW_MAJOR if col_c else la, lb if col_c else Layout.COLUMN_MAJOR, lc,
+                                    add_identity=operator.add_identity, mul_identity=operator.mul_identity)
         self.group, self.rank, self.world = group, int(rank), int(world)
         if self.world > 1:
             shared_elems = (m * k) if col_c else (k * n)
@@ -248,6 +258,18 @@ class HostSrgemm:
             arrived.record(self.s_comm)
         return arrived
 
+    def _pack_shared(self, shared_dev, p: int) -> None:
+        """K piece p of the shared operand (all of it when there is one piece), which the compute stream has just
+        been told to wait for, into the K-contiguous copy the launches read."""
+        if self.packed is None:
+            return
+        kp = self.k // self.k_pieces
+        rows, ld = (self.m, self.lda) if self.col_c else (self.n, self.ldb)
+        st = pack_k_contiguous(self.op.dtype, shared_dev.data_ptr() + p * kp * ld * self.es, ld, False, rows, kp,
+                               self.packed.data_ptr() + p * kp * self.es, self.k, self.s_run)
+        if st != Status.kSuccess:
+            raise RuntimeError(f"packing the shared operand failed: {st!r}")
+
     def _chunk_args(self, j: int):
         """Arguments of chunk j and the element ranges of B (or A), C and D it touches."""
         m, n, k = self.m, self.n, self.k
@@ -255,23 +277,26 @@ class HostSrgemm:
         if self.col_c:
             moving, fixed = slice(l0 * k, (l0 + w) * k), None             # columns of B
             out = slice(l0 * m, (l0 + w) * m)
-            args = Arguments((m, w, k), (self.dA, self.lda), (self.dB.data_ptr() + moving.start * self.es, self.ldb),
+            shared = (self.packed, k) if self.packed is not None else (self.dA, self.lda)
+            args = Arguments((m, w, k), shared, (self.dB.data_ptr() + moving.start * self.es, self.ldb),
                              (self.dC.data_ptr() + out.start * self.es, self.ldc),
                              (self.dD.data_ptr() + out.start * self.es, self.ldc), (self.alpha, self.beta))
         else:
             moving = slice(l0 * k, (l0 + w) * k)                           # rows of A
             out = slice(l0 * n, (l0 + w) * n)
-            args = Arguments((w, n, k), (self.dA.data_ptr() + moving.start * self.es, self.lda), (self.dB, self.ldb),
+            shared = (self.packed, k) if self.packed is not None else (self.dB, self.ldb)
+            args = Arguments((w, n, k), (self.dA.data_ptr() + moving.start * self.es, self.lda), shared,
                              (self.dC.data_ptr() + out.start * self.es, self.ldc),
                              (self.dD.data_ptr() + out.start * self.es, self.ldc), (self.alpha, self.beta))
         return args, moving, out
 
     def _launch(self, args, extras, what: str) -> None:
         torch = self.torch
+        op = self.op_packed if self.packed is not None else self.op
         with torch.cuda.stream(self.s_run):
-            st = self.op.initialize(args, self.workspace, self.s_run)
+            st = op.initialize(args, self.workspace, self.s_run)
             if st == Status.kSuccess:
-                st = self.op.run_push(extras, self.s_run) if extras else self.op.run(self.s_run)
+                st = op.run_push(extras, self.s_run) if extras else op.run(self.s_run)
             if st != Status.kSuccess:
                 raise RuntimeError(f"SRGEMM failed on {what}: {st!r}")
             self.launches += 1
@@ -285,12 +310,16 @@ class HostSrgemm:
         self.s_run.wait_event(inputs)
         for p in range(self.k_pieces):
             self.s_run.wait_event(first_piece if p == 0 else self._bring_shared_piece(shared_dev, shared_host, p))
+            self._pack_shared(shared_dev, p)
+            # a K piece of the packed shared operand is a run of kp elements in every line: offset p * kp
             if self.col_c:      # A column-major: K piece = columns of A; B chunk column-major: K piece = rows of B
-                a = (_address(args.ref_A[0]) + p * kp * self.lda * es, self.lda)
+                a = ((_address(args.ref_A[0]) + p * kp * es, self.k) if self.packed is not None
+                     else (_address(args.ref_A[0]) + p * kp * self.lda * es, self.lda))
                 b = (_address(args.ref_B[0]) + p * kp * es, self.ldb)
             else:               # A chunk row-major: K piece = columns of A; B row-major: K piece = rows of B
                 a = (_address(args.ref_A[0]) + p * kp * es, self.lda)
-                b = (_address(args.ref_B[0]) + p * kp * self.ldb * es, self.ldb)
+                b = ((_address(args.ref_B[0]) + p * kp * es, self.k) if self.packed is not None
+                     else (_address(args.ref_B[0]) + p * kp * self.ldb * es, self.ldb))
             first, last = p == 0, p == self.k_pieces - 1
             c = args.ref_C if first else args.ref_D
             beta = self.beta if first else self.op.mul_identity
@@ -314,7 +343,8 @@ class HostSrgemm:
             (cm, cn, ck) = whole.problem_size
             shapes = [whole, Arguments((cm, cn, ck // self.k_pieces), whole.ref_A, whole.ref_B, whole.ref_C,
                                        whole.ref_D, whole.epilogue)]
-            need = max(self.op.get_optional_workspace_size(a) for a in shapes)
+            need = max((self.op_packed if self.packed is not None else self.op).get_optional_workspace_size(a)
+                       for a in shapes)
             self.workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=self.device)
         whole_shared = None
         if self.k_pieces == 1 and not self.shared_on_device:
@@ -347,6 +377,8 @@ class HostSrgemm:
                 self.s_run.wait_event(arrived)
                 if whole_shared is not None:
                     self.s_run.wait_event(whole_shared)
+                if j == 0 and self.k_pieces == 1:
+                    self._pack_shared(shared_dev, 0)
                 self._launch(args, extras, f"chunk {j}")
             done.record(self.s_run)
             self.s_out.wait_event(done)

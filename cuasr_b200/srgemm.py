@@ -197,6 +197,16 @@ def srgemm_splitk_static(operator: _Operator, args: Arguments, stream=None) -> S
     return Status(lib.cuasr_b200_srgemm_splitk_static(ctypes.byref(operator._desc), ctypes.byref(packed)))
 
 
+def pack_k_contiguous(dtype: DType, src, ld_src: int, src_k_contiguous: bool, rows: int, k: int, dst, ld_dst: int,
+                      stream=None) -> Status:
+    """cuasr_b200_pack_k_contiguous: copies a rows x k operand (tensors or device addresses) into storage that is
+    contiguous along k, dst[r * ld_dst + kk], from src[r + kk * ld_src] or (src_k_contiguous) src[r * ld_src + kk].
+    A column-major A packed this way is passed on as a row-major A with leading dimension ld_dst."""
+    return Status(_lib.load().cuasr_b200_pack_k_contiguous(int(dtype), _ptr(src), int(ld_src), int(bool(src_k_contiguous)),
+                                                           int(rows), int(k), _ptr(dst), int(ld_dst),
+                                                           _stream_handle(stream)))
+
+
 def device_status(stream=None) -> int:
     """Synchronises `stream` and returns the device-side status word (0 = ok)."""
     return int(_lib.load().cuasr_b200_device_status(_stream_handle(stream)))

@@ -161,6 +161,18 @@ CUASR_B200_API int cuasr_b200_srgemm_splitk(const cuasr_b200_desc_t *desc, const
 #define CUASR_B200_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u + 4096u)
 CUASR_B200_API int cuasr_b200_srgemm_splitk_static(const cuasr_b200_desc_t *desc, const cuasr_b200_args_t *args);
 
+/* Copies a rows x k operand of 4- or 8-byte elements (dtype: any cuasr_dtype_t) into storage that is contiguous
+ * along k: the element with row index r and contraction index kk, found at src[r + kk * ld_src]
+ * (src_k_contiguous == 0: a column-major A, a row-major B) or at src[r * ld_src + kk] (src_k_contiguous != 0), goes
+ * to dst[r * ld_dst + kk].  Any leading dimensions (ld_dst >= k) and alignments; src and dst must not overlap.
+ * New in this library.  The kernels run fastest on operands that are contiguous along k and otherwise make such
+ * a copy themselves, per call, when they are given the optional workspace; a caller that multiplies by the same
+ * column-major A (row-major B) many times can make the copy once with this call and pass it as a row-major A
+ * (column-major B) with leading dimension ld_dst.  The result of the product is the same bits either way.
+ * Enqueues on `stream` and returns. */
+CUASR_B200_API int cuasr_b200_pack_k_contiguous(int32_t dtype, const void *src, int64_t ld_src, int32_t src_k_contiguous,
+                                                int32_t rows, int32_t k, void *dst, int64_t ld_dst, void *stream);
+
 /* Reads (and clears) the device-side status word of the current device after synchronising `stream`:
  * 0 = every kernel of this library ran to completion; otherwise a bounded wait inside a kernel expired
  * (1: tile never arrived, 2: stage never released, 3: peer flag never set).  This call blocks. */

@@ -336,9 +336,56 @@ def test_host_buffer_pipeline_equals_one_shot(cuda_device, layouts):
         assert np.array_equal(hD.numpy(), want)
     chunked = layouts in ((COL, COL, COL), (ROW, COL, ROW), (ROW, ROW, ROW))
     assert pipe.chunks == (4 if chunked else 1)
+    # a shared operand whose lines do not run along k is packed once for all chunks, not once per launch
+    assert (pipe.packed is not None) == (layouts in ((COL, COL, COL), (ROW, ROW, ROW)))
     # the first chunk runs as K pieces where the K range of the shared operand is a run of whole storage lines
     assert pipe.k_pieces == (4 if layouts in ((COL, COL, COL), (ROW, ROW, ROW)) else 1)
     assert HostSrgemm(Srgemm(*RINGS["plus_multiplies"], dt, *layouts), m, n, k, 1.0, 1.0, cuda_device).k_pieces == 1
+    assert device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [DType.F32, DType.F64, DType.S32])
+def test_pack_k_contiguous(cuda_device, dt):
+    """cuasr_b200_pack_k_contiguous: both source forms, ragged sizes, padded leading dimensions on either side; the
+    padding of the destination stays as it was; a product fed the packed copy as a row-major A has the same bits."""
+    import torch
+    from cuasr_b200 import pack_k_contiguous
+    rng = np.random.default_rng(5)
+    np_t = util.NUMPY_DTYPE[dt]
+    tdt = {DType.F32: torch.float32, DType.F64: torch.float64, DType.S32: torch.int32}[dt]
+    for rows, k, ld_src_pad, ld_dst_pad in [(130, 67, 3, 5), (1, 9, 0, 0), (513, 1, 2, 3), (256, 256, 0, 0)]:
+        x = rng.integers(-50, 50, size=(rows, k)).astype(np_t)                 # x[r, kk]
+        for src_k_contiguous in (False, True):
+            ld_src = (k if src_k_contiguous else rows) + ld_src_pad
+            lines = rows if src_k_contiguous else k
+            src = np.full((lines, ld_src), 77, dtype=np_t)
+            src[:, :ld_src - ld_src_pad] = x if src_k_contiguous else x.T
+            ld_dst = k + ld_dst_pad
+            d_src = torch.from_numpy(src).cuda()
+            d_dst = torch.full((rows, ld_dst), -9, dtype=tdt, device="cuda")
+            assert pack_k_contiguous(dt, d_src, ld_src, src_k_contiguous, rows, k, d_dst, ld_dst) == Status.kSuccess
+            torch.cuda.synchronize()
+            got = d_dst.cpu().numpy()
+            assert np.array_equal(got[:, :k], x) and np.all(got[:, k:] == -9), (rows, k, src_k_contiguous)
+    assert pack_k_contiguous(dt, 0, 8, False, 8, 8, 4096, 8) == Status.kErrorInvalidProblem
+    assert pack_k_contiguous(dt, 4096, 8, False, 8, 8, 8192, 7) == Status.kErrorInvalidProblem       # ld_dst < k
+    assert pack_k_contiguous(dt, 4096, 7, False, 8, 8, 8192, 8) == Status.kErrorInvalidProblem       # ld_src < rows
+    assert pack_k_contiguous(dt, 4098, 8, False, 8, 8, 8192, 8) == Status.kErrorMisalignedOperand
+    if dt == DType.F32:
+        m, n, k = 384, 256, 320
+        A, lda = util.make_matrix(rng, dt, COL, m, k)
+        B, ldb = util.make_matrix(rng, dt, COL, k, n)
+        C, ldc = util.make_matrix(rng, dt, COL, m, n)
+        dA, dB, dC = (torch.from_numpy(t).cuda() for t in (A, B, C))
+        dD, dD2 = torch.empty_like(dC), torch.empty_like(dC)
+        packed = torch.empty(m * k, dtype=torch.float32, device="cuda")
+        assert pack_k_contiguous(dt, dA, lda, False, m, k, packed, k) == Status.kSuccess
+        plain = Srgemm(*RINGS["minimum_plus"], dt, COL, COL, COL)
+        assert plain(Arguments((m, n, k), (dA, lda), (dB, ldb), (dC, ldc), (dD, ldc), (0.0, 0.0))) == Status.kSuccess
+        rowa = Srgemm(*RINGS["minimum_plus"], dt, ROW, COL, COL)
+        assert rowa(Arguments((m, n, k), (packed, k), (dB, ldb), (dC, ldc), (dD2, ldc), (0.0, 0.0))) == Status.kSuccess
+        torch.cuda.synchronize()
+        assert torch.equal(dD, dD2)
     assert device_status() == 0
 
 
