@@ -107,7 +107,8 @@ CUASR_B200_API int cuasr_b200_apsp_shard_squaring(const cuasr_b200_apsp_shard_ar
  *   waiting when the others get there); every GPU updates its piece of the row panel and its own columns in
  *   place.  The closure ends up in buf0 (*result_buffer = 0), distributed as it came.  The workspace is REQUIRED:
  *   cuasr_b200_apsp_multi_workspace_size bytes per GPU, 256-byte aligned.
- * The call blocks the calling host thread until the solve is done.  Status: CUASR_STATUS_ERROR_NOT_SUPPORTED when a
+ * The call blocks the calling host thread until the solve is done; peer access between the GPUs is switched on by
+ * it and left on.  Status: CUASR_STATUS_ERROR_NOT_SUPPORTED when a
  * GPU cannot reach a peer's memory, otherwise the first error any GPU met; `device_status` (n_devices entries, may
  * be NULL) receives each GPU's cuasr_b200_device_status after the solve. */
 typedef struct cuasr_b200_apsp_multi_args {
