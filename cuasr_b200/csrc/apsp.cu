@@ -518,17 +518,24 @@ int cuasr_b200_apsp_multi(const cuasr_b200_apsp_multi_args_t* a) {
       // phase 2, my piece of the row panel: P_row = min(D[K, mine], D[K, K]* (x) D[K, mine])
       const char* rows = D + static_cast<size_t>(k0) * es;
       int st = product(b, cols, b, p_col + static_cast<size_t>(k0) * es, n, rows, a->ldd, rows, a->ldd, p_row, b, 0, nullptr);
+      // phase 3: my columns [c0, c1) through the two panels, in place (the operands are copies)
+      auto update = [&](size_t c0, size_t c1) {
+        if (c1 <= c0) return static_cast<int>(CUASR_STATUS_SUCCESS);
+        char* part = D + c0 * a->ldd * es;
+        return product(n, static_cast<int>(c1 - c0), b, p_col, n, static_cast<char*>(p_row) + c0 * b * es, b, part,
+                       a->ldd, part, a->ldd, 0, nullptr);
+      };
       if (st == CUASR_STATUS_SUCCESS && kb + 1 < blocks && (kb + 1) % G == g) {
         // the next block is mine: phase 3 on it alone, then its panel goes out before the rest of phase 3
         const size_t lc = static_cast<size_t>((kb + 1) / G) * b;
-        char* blk = D + lc * a->ldd * es;
-        st = product(n, b, b, p_col, n, static_cast<char*>(p_row) + lc * b * es, b, blk, a->ldd, blk, a->ldd, 0, nullptr);
+        st = update(lc, lc + b);
         if (st == CUASR_STATUS_SUCCESS) st = make_panel(kb + 1);
         wait_for_push = true;
+        if (st == CUASR_STATUS_SUCCESS) st = update(0, lc);
+        if (st == CUASR_STATUS_SUCCESS) st = update(lc + b, cols);
+      } else if (st == CUASR_STATUS_SUCCESS) {
+        st = update(0, cols);
       }
-      // phase 3: my columns through the two panels, in place (the operands are copies).  A block that was brought
-      // up to date above is simply visited again: min(D, P_col (x) P_row) changes nothing the second time.
-      if (st == CUASR_STATUS_SUCCESS) st = product(n, cols, b, p_col, n, p_row, b, D, a->ldd, D, a->ldd, 0, nullptr);
       if (st == CUASR_STATUS_SUCCESS && cudaEventRecord(done[kb % kPanelBuffers], stream) != cudaSuccess)
         st = CUASR_STATUS_ERROR_INTERNAL;
       if (st != CUASR_STATUS_SUCCESS) fail(st);
