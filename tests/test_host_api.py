@@ -119,3 +119,20 @@ def test_numa_local_leaves_the_process_as_it_found_it():
         inside = os.sched_getaffinity(0)
         assert inside <= before and (where.node is not None or inside == before)
     assert os.sched_getaffinity(0) == before
+
+
+def test_pack_k_contiguous_checks_its_arguments_before_touching_a_device():
+    from cuasr_b200 import pack_k_contiguous
+    ok = dict(dtype=DType.F32, src=4096, ld_src=16, src_k_contiguous=False, rows=16, k=8, dst=8192, ld_dst=8)
+    call = lambda **kw: pack_k_contiguous(**dict(ok, **kw))
+    assert call(src=0) == Status.kErrorInvalidProblem
+    assert call(dst=0) == Status.kErrorInvalidProblem
+    assert call(rows=0) == Status.kErrorInvalidProblem
+    assert call(ld_dst=7) == Status.kErrorInvalidProblem                      # shorter than a line of the copy
+    assert call(ld_src=15) == Status.kErrorInvalidProblem                     # shorter than a line of the source
+    assert call(src_k_contiguous=True, ld_src=7) == Status.kErrorInvalidProblem
+    assert call(src=4098) == Status.kErrorMisalignedOperand
+    assert call(dtype=DType.F64, dst=8196) == Status.kErrorMisalignedOperand
+    import ctypes
+    from cuasr_b200 import _lib
+    assert _lib.load().cuasr_b200_pack_k_contiguous(99, 4096, 16, 0, 16, 8, 8192, 8, None) == int(Status.kErrorInvalidDataType)
